@@ -60,10 +60,11 @@ def architecture_name(raw: dict) -> str:
     archs = raw.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
-    mt = raw.get("model_type")
-    if isinstance(mt, str):
-        return mt
-    raise ConfigError("config.json names no architecture (neither 'architectures' nor 'model_type')")
+    for key in ("architecture", "model_type"):       # a single name under 'architecture' is how some designs say it
+        name = raw.get(key)
+        if isinstance(name, str):
+            return name
+    raise ConfigError("config.json names no architecture (none of 'architectures', 'architecture', 'model_type')")
 
 
 def load_config(model_dir: str) -> ModelConfig:

@@ -200,9 +200,11 @@ def tma_decode_supported(hd: int, group: int, page_tokens: int) -> bool:
 
 
 def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan: FlashPlan,
-        allow_tma: bool = True) -> bool:
+        allow_tma: bool = True, sink: bool = False) -> bool:
     from . import gemm_fast, ops
     if not supported(hd, H // G) or plan is None:
+        return False
+    if sink:            # the flash kernels have no sink term yet: the generic kernel takes the step
         return False
     lib = build.load("attention_flash")
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)

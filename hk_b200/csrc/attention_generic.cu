@@ -7,6 +7,9 @@
 // the keys round-robin, each keeping an online softmax state (max, sum, weighted values); the
 // four states are merged in a fixed order.  Nothing depends on which other tokens are in the
 // batch, so the result at a position is the same under every way of cutting the work.
+// Values may be narrower than keys (`vd` <= hd: pages [page][G][page_tokens][vd], out [n, H * vd]).  With
+// `sink` = 1 the softmax has one more term in its denominator, a key whose score is 0 and that has no value:
+// p_j = exp(s_j) / (1 + sum exp(s_j)).
 //
 // Reference counterpart: `attention`, src/cuda_device.zig:1494-1594 (block per (token, head),
 // warp per position, online softmax); scale on q first: src/engine/attention_kernel.zig:109.
@@ -23,10 +26,10 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                          const T* __restrict__ v_pages, const int* __restrict__ block_table,
                          int table_stride, const int* __restrict__ positions,
                          const int* __restrict__ slot_of_token, T* __restrict__ out, int H, int G, int hd,
-                         int page_tokens, int window, float scale) {
-  extern __shared__ float smem[];  // [AG_WARPS][hd] values, then [AG_WARPS] max, [AG_WARPS] sum
+                         int page_tokens, int window, float scale, int vd, int sink) {
+  extern __shared__ float smem[];  // [AG_WARPS][vd] values, then [AG_WARPS] max, [AG_WARPS] sum
   float* acc_s = smem;
-  float* m_s = smem + AG_WARPS * hd;
+  float* m_s = smem + AG_WARPS * vd;
   float* l_s = m_s + AG_WARPS;
 
   int t = blockIdx.x / H, h = blockIdx.x % H;
@@ -48,9 +51,9 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
   for (int j = lo + wid; j <= pos; j += AG_WARPS) {
     int page = bt[j / page_tokens];
     if (page < 0) continue;  // never scheduled by the host; keeps the reads in bounds
-    size_t off = (((size_t)page * G + g) * page_tokens + (j % page_tokens)) * hd;
-    const T* kp = k_pages + off;
-    const T* vp = v_pages + off;
+    const size_t at = ((size_t)page * G + g) * page_tokens + (j % page_tokens);
+    const T* kp = k_pages + at * hd;
+    const T* vp = v_pages + at * vd;
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < AG_MAX_PER_LANE; ++i) {
@@ -65,34 +68,35 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
 #pragma unroll
     for (int i = 0; i < AG_MAX_PER_LANE; ++i) {
       int d = lane + 32 * i;
-      if (d < hd) acc[i] = acc[i] * corr + p * to_f32<T>(vp[d]);
+      if (d < vd) acc[i] = acc[i] * corr + p * to_f32<T>(vp[d]);
     }
     m = mn;
   }
 #pragma unroll
   for (int i = 0; i < AG_MAX_PER_LANE; ++i) {
     int d = lane + 32 * i;
-    if (d < hd) acc_s[wid * hd + d] = acc[i];
+    if (d < vd) acc_s[wid * vd + d] = acc[i];
   }
   if (lane == 0) {
     m_s[wid] = m;
     l_s[wid] = l;
   }
   __syncthreads();
-  float mm = m_s[0];
+  float mm = sink ? 0.f : m_s[0];   // the sink's score takes part in the maximum
 #pragma unroll
-  for (int w = 1; w < AG_WARPS; ++w) mm = fmaxf(mm, m_s[w]);
+  for (int w = sink ? 0 : 1; w < AG_WARPS; ++w) mm = fmaxf(mm, m_s[w]);
   float f[AG_WARPS], lt = 0.f;
 #pragma unroll
   for (int w = 0; w < AG_WARPS; ++w) {
     f[w] = m_s[w] == -CUDART_INF_F ? 0.f : expf(m_s[w] - mm);
     lt += l_s[w] * f[w];
   }
-  T* op = out + ((size_t)t * H + h) * hd;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+  if (sink) lt += expf(-mm);
+  T* op = out + ((size_t)t * H + h) * vd;
+  for (int d = threadIdx.x; d < vd; d += blockDim.x) {
     float a = 0.f;
 #pragma unroll
-    for (int w = 0; w < AG_WARPS; ++w) a += acc_s[w * hd + d] * f[w];
+    for (int w = 0; w < AG_WARPS; ++w) a += acc_s[w * vd + d] * f[w];
     op[d] = from_f32<T>(a / lt);
   }
 }
@@ -100,20 +104,20 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
 HK_API int hk_attention_generic(const void* q, const void* k_pages, const void* v_pages, int dtype,
                                 const int* block_table, int table_stride, const int* positions,
                                 const int* slot_of_token, void* out, int n, int H, int G, int hd,
-                                int page_tokens, int window, float scale, void* stream) {
+                                int page_tokens, int window, float scale, int vd, int sink, void* stream) {
   if (n <= 0) return 0;
-  if (hd > 32 * AG_MAX_PER_LANE || hd < 1 || G < 1 || H % G != 0) return HK_ERR_UNSUPPORTED;
+  if (hd > 32 * AG_MAX_PER_LANE || hd < 1 || G < 1 || H % G != 0 || vd < 1 || vd > hd) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-  size_t smem = (size_t)(AG_WARPS * hd + 2 * AG_WARPS) * sizeof(float);
+  size_t smem = (size_t)(AG_WARPS * vd + 2 * AG_WARPS) * sizeof(float);
   unsigned blocks = (unsigned)((long long)n * H);
   if (dtype == HK_F32)
     attention_generic_kernel<float><<<blocks, AG_WARPS * 32, smem, s>>>(
         (const float*)q, (const float*)k_pages, (const float*)v_pages, block_table, table_stride, positions,
-        slot_of_token, (float*)out, H, G, hd, page_tokens, window, scale);
+        slot_of_token, (float*)out, H, G, hd, page_tokens, window, scale, vd, sink);
   else if (dtype == HK_BF16)
     attention_generic_kernel<bf16><<<blocks, AG_WARPS * 32, smem, s>>>(
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, positions,
-        slot_of_token, (bf16*)out, H, G, hd, page_tokens, window, scale);
+        slot_of_token, (bf16*)out, H, G, hd, page_tokens, window, scale, vd, sink);
   else
     return HK_ERR_UNSUPPORTED;
   return hk_launch_status();

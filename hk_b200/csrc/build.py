@@ -41,16 +41,29 @@ LIBRARIES: Dict[str, str] = {
     "gemm_stream": "gemm_stream.cu",
     "attention_flash": "attention_flash.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
+    "recurrent": "recurrent.cu",       # scans of the recurrent mixers (delta rule, minGRU)
+    "routed": "routed.cu",             # a feed-forward of experts: route, sort, grouped products, combine
     "runtime": "runtime.cpp",          # host only: the cache's books (no GPU code, no CUDA headers)
 }
 
 
-def libraries_for(bfloat16: bool) -> List[str]:
+def libraries_for(bfloat16: bool, model=None) -> List[str]:
     """The kernel libraries a model needs: the generic ones always (the 32-bit path, and shapes the fast kernels
-    refuse), the tensor-core and streaming ones only when it computes in bfloat16."""
+    refuse), the tensor-core and streaming ones only when it computes in bfloat16, and whatever the model's parts
+    name in their `kernel_libraries` (a recurrent mixer's scans, a routed feed-forward's kernels)."""
     needed = ["elementwise", "gemm_generic", "attention_generic"]
     if bfloat16:
         needed += ["gemm_smallm", "gemm_stream", "gemm_tc", "attention_flash", "attention_prefill_tc"]
+
+    def walk(part):
+        for name in getattr(part, "kernel_libraries", ()):
+            if name not in needed:
+                needed.append(name)
+        for c in part.children():
+            walk(c)
+
+    if model is not None:
+        walk(model)
     return needed
 
 

@@ -212,8 +212,11 @@ HK_API int hk_rms_norm(const float* x, const float* w, const int* rows, void* ou
 // `bias` (or null) [(H + 2G) * hd] is added to the projection output first.  `pairing` 0 rotates dims
 // (i, i + rot/2) ("rotate-half"), 1 rotates dims (2i, 2i + 1) ("adjacent"); both read angle i of the tables.
 // Page of a token: block_table[slot_of_token[t]][pos / page_tokens]; the cache layout is
-// [page][G][page_tokens][hd].  With write_kv == 0 only q is produced (a layer that reads
-// another layer's cache).
+// [page][G][page_tokens][hd] for keys and [page][G][page_tokens][vd] for values.  With write_kv == 0 only q is
+// produced (a layer that reads another layer's cache).
+// `norm_after` = 1 moves the per-head norm behind the rotation, where a null weight means a weight of ones
+// (x over its root mean square).  `tied_v` = 1: the projection has no v heads (a row holds H + G heads) and a
+// token's value is its key as projected, before rotation and norm, of which the first `vd` dims are kept.
 #define QKR_MAX_HD 256
 #define QKR_WARPS 4
 
@@ -224,17 +227,18 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
     const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
-    int write_kv, const float* __restrict__ bias, int pairing) {
+    int write_kv, const float* __restrict__ bias, int pairing, int norm_after, int tied_v, int vd) {
   __shared__ float buf[QKR_WARPS][QKR_MAX_HD];
   pdl_launch_dependents();
   pdl_wait();
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  int heads_total = H + (write_kv ? 2 * G : 0);
+  const int kv_heads = tied_v ? G : 2 * G;
+  int heads_total = H + (write_kv ? kv_heads : 0);
   long long item = (long long)blockIdx.x * QKR_WARPS + wid;
   if (item >= (long long)n * heads_total) return;
   int t = (int)(item / heads_total);
   int hh = (int)(item % heads_total);
-  const float* src = qkv + (size_t)t * (H + 2 * G) * hd + (size_t)hh * hd;
+  const float* src = qkv + (size_t)t * (H + kv_heads) * hd + (size_t)hh * hd;
   float* v = buf[wid];
   float ss = 0.f;
   for (int i = lane; i < hd; i += 32) {
@@ -246,9 +250,18 @@ __global__ void qk_norm_rope_kv_write_kernel(
   __syncwarp();
   int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);  // q, k, v
   int pos = positions[t];
+  int page = -1;
+  if (kind != 0) {
+    page = block_table[(size_t)slot_of_token[t] * table_stride + pos / page_tokens];
+    if (page < 0) return;  // the host never schedules this; keeps a stale table from writing out of bounds
+    if (kind == 1 && tied_v) {   // the value is the key as projected
+      T* vdst = v_pages + (((size_t)page * G + (hh - H)) * page_tokens + (pos % page_tokens)) * vd;
+      for (int i = lane; i < vd; i += 32) vdst[i] = from_f32<T>(v[i]);
+    }
+  }
   if (kind != 2) {
     const float* w = kind == 0 ? q_w : k_w;
-    if (w) {
+    if (w && !norm_after) {
       ss = warp_sum(ss);
       float inv = 1.0f / sqrtf(ss / (float)hd + eps);
       for (int i = lane; i < hd; i += 32) v[i] = v[i] * inv * w[i];
@@ -267,18 +280,26 @@ __global__ void qk_norm_rope_kv_write_kernel(
       }
       __syncwarp();
     }
+    if (norm_after) {
+      float s2 = 0.f;
+      for (int i = lane; i < hd; i += 32) s2 = fmaf(v[i], v[i], s2);
+      s2 = warp_sum(s2);
+      const float inv = 1.0f / sqrtf(s2 / (float)hd + eps);
+      for (int i = lane; i < hd; i += 32) v[i] = v[i] * inv * (w ? w[i] : 1.0f);
+      __syncwarp();
+    }
   }
   T* dst;
+  int width = hd;
   if (kind == 0) {
     dst = q_out + (size_t)t * H * hd + (size_t)hh * hd;
+  } else if (kind == 1) {
+    dst = k_pages + (((size_t)page * G + (hh - H)) * page_tokens + (pos % page_tokens)) * hd;
   } else {
-    int g = kind == 1 ? hh - H : hh - H - G;
-    int page = block_table[(size_t)slot_of_token[t] * table_stride + pos / page_tokens];
-    if (page < 0) return;  // the host never schedules this; keeps a stale table from writing out of bounds
-    T* base = kind == 1 ? k_pages : v_pages;
-    dst = base + (((size_t)page * G + g) * page_tokens + (pos % page_tokens)) * hd;
+    width = vd;
+    dst = v_pages + (((size_t)page * G + (hh - H - G)) * page_tokens + (pos % page_tokens)) * vd;
   }
-  for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(v[i]);
+  for (int i = lane; i < width; i += 32) dst[i] = from_f32<T>(v[i]);
 }
 
 // The same for head sizes up to 128 that are a multiple of 4 (and a rotary width that is a multiple of 8):
@@ -293,18 +314,19 @@ qk_norm_rope_kv_write_vec_kernel(
     const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
     const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
-    int write_kv, const float* __restrict__ bias, int pairing) {
+    int write_kv, const float* __restrict__ bias, int pairing, int norm_after, int tied_v, int vd) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const int heads_total = H + (write_kv ? 2 * G : 0);
+  const int kv_heads = tied_v ? G : 2 * G;
+  const int heads_total = H + (write_kv ? kv_heads : 0);
   const long long item = (long long)blockIdx.x * QKV_WARPS + wid;
   if (item >= (long long)n * heads_total) return;
   const int t = (int)(item / heads_total);
   const int hh = (int)(item % heads_total);
   const int d0 = lane * 4;
   const bool active = d0 < hd;
-  const float* src = qkv + (size_t)t * (H + 2 * G) * hd + (size_t)hh * hd;
+  const float* src = qkv + (size_t)t * (H + kv_heads) * hd + (size_t)hh * hd;
   float4 v = active ? *reinterpret_cast<const float4*>(src + d0) : make_float4(0.f, 0.f, 0.f, 0.f);
   if (bias && active) {
     const float4 b = *reinterpret_cast<const float4*>(bias + (size_t)hh * hd + d0);
@@ -312,9 +334,21 @@ qk_norm_rope_kv_write_vec_kernel(
   }
   const int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);
   const int pos = positions[t];
+  int page = 0;
+  if (kind != 0) page = block_table[(size_t)slot_of_token[t] * table_stride + pos / page_tokens];
+  if (kind == 1 && tied_v && page >= 0 && d0 < vd) {      // the value is the key as projected
+    T* vdst = v_pages + (((size_t)page * G + (hh - H)) * page_tokens + (pos % page_tokens)) * vd;
+    if (sizeof(T) == 4) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(vdst) + d0) = v;
+    } else {
+      __nv_bfloat162 lo2 = __floats2bfloat162_rn(v.x, v.y), hi2 = __floats2bfloat162_rn(v.z, v.w);
+      *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(vdst) + d0) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&lo2), *reinterpret_cast<uint32_t*>(&hi2));
+    }
+  }
   if (kind != 2) {
     const float* w = kind == 0 ? q_w : k_w;
-    if (w) {
+    if (w && !norm_after) {
       float ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
       ss = warp_sum(ss);
       const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
@@ -352,17 +386,25 @@ qk_norm_rope_kv_write_vec_kernel(
           v = make_float4(p.x * sn.x + v.x * c.x, p.y * sn.y + v.y * c.y, p.z * sn.z + v.z * c.z, p.w * sn.w + v.w * c.w);
       }
     }
+    if (norm_after) {
+      float ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+      if (active) {
+        const float4 g = w ? *reinterpret_cast<const float4*>(w + d0) : make_float4(1.f, 1.f, 1.f, 1.f);
+        v = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+      }
+    }
   }
-  if (!active) return;
+  if (!active || page < 0) return;
   T* dst;
   if (kind == 0) {
     dst = q_out + (size_t)t * H * hd + (size_t)hh * hd;
+  } else if (kind == 1) {
+    dst = k_pages + (((size_t)page * G + (hh - H)) * page_tokens + (pos % page_tokens)) * hd;
   } else {
-    const int g = kind == 1 ? hh - H : hh - H - G;
-    const int page = block_table[(size_t)slot_of_token[t] * table_stride + pos / page_tokens];
-    if (page < 0) return;
-    T* base = kind == 1 ? k_pages : v_pages;
-    dst = base + (((size_t)page * G + g) * page_tokens + (pos % page_tokens)) * hd;
+    if (d0 >= vd) return;
+    dst = v_pages + (((size_t)page * G + (hh - H - G)) * page_tokens + (pos % page_tokens)) * vd;
   }
   if (sizeof(T) == 4) {
     *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + d0) = v;
@@ -378,34 +420,36 @@ HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, co
                                     int rot, const int* positions, const int* slot_of_token,
                                     const int* block_table, int table_stride, void* k_pages,
                                     void* v_pages, int n, int H, int G, int hd, int page_tokens,
-                                    int write_kv, const float* bias, int pairing, void* stream) {
+                                    int write_kv, const float* bias, int pairing, int norm_after, int tied_v, int vd,
+                                    void* stream) {
   if (n <= 0) return 0;
   if (hd > QKR_MAX_HD || hd < 2 || rot > hd || (rot & 1) || pairing < 0 || pairing > 1) return HK_ERR_UNSUPPORTED;
+  if (vd < 1 || vd > hd) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-  long long items = (long long)n * (H + (write_kv ? 2 * G : 0));
+  long long items = (long long)n * (H + (write_kv ? (tied_v ? G : 2 * G) : 0));
   const bool aligned = ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)q_w |
                           (uintptr_t)k_w | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)bias) & 15) == 0);
-  if (hd <= 128 && (hd & 3) == 0 && (rot & 7) == 0 && aligned) {
+  if (hd <= 128 && (hd & 3) == 0 && (vd & 3) == 0 && (rot & 7) == 0 && aligned) {
     unsigned vblocks = (unsigned)((items + QKV_WARPS - 1) / QKV_WARPS);
     if (dtype == HK_F32)
       return hk_launch_pdl(qk_norm_rope_kv_write_vec_kernel<float>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (float*)q_out,
                        q_w, k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (float*)k_pages,
-                       (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
+                       (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd);
     if (dtype == HK_BF16)
       return hk_launch_pdl(qk_norm_rope_kv_write_vec_kernel<bf16>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
                        k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (bf16*)k_pages,
-                       (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
+                       (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd);
     return HK_ERR_UNSUPPORTED;
   }
   unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
   if (dtype == HK_F32)
     return hk_launch(qk_norm_rope_kv_write_kernel<float>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, qkv, (float*)q_out, q_w,
                          k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (float*)k_pages,
-                         (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
+                         (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd);
   if (dtype == HK_BF16)
     return hk_launch(qk_norm_rope_kv_write_kernel<bf16>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
                          k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (bf16*)k_pages,
-                         (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
+                         (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd);
   return HK_ERR_UNSUPPORTED;
 }
 
@@ -447,5 +491,114 @@ HK_API int hk_swiglu(const float* gu, void* out, int out_dtype, int n, int F, in
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (out_dtype == HK_F32) return hk_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, s, gu, (float*)out, total, F, block);
   if (out_dtype == HK_BF16) return hk_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, gu, (bf16*)out, total, F, block);
+  return HK_ERR_UNSUPPORTED;
+}
+
+// ----------------------------------------------------------------------------- norm of a sublayer's output, added
+// residual[r, :] += y[r, :] * rsqrt(mean(y^2) + eps) * w: the norm AFTER a mixer or feed-forward of a layer that
+// norms both sides of its sublayers, fused with the residual sum (which stays fp32).  Same summation order as
+// `rms_norm_kernel`.
+__global__ void rms_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ residual,
+                                    int d, float eps) {
+  __shared__ float warp_part[32];
+  __shared__ float inv_s;
+  const int r = blockIdx.x;
+  const float* src = y + (size_t)r * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = src[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) warp_part[wid] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < nw; ++i) tot += warp_part[i];
+    inv_s = 1.0f / sqrtf(tot / (float)d + eps);
+  }
+  __syncthreads();
+  const float inv = inv_s;
+  float* dst = residual + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] += src[i] * inv * w[i];
+}
+
+HK_API int hk_rms_norm_add(const float* y, const float* w, float* residual, int n, int d, float eps, void* stream) {
+  if (n <= 0) return 0;
+  return hk_launch(rms_norm_add_kernel, dim3((unsigned)n), dim3(d >= 2048 ? 256 : 128), 0, (cudaStream_t)stream, y, w, residual, d,
+                   eps);
+}
+
+// ----------------------------------------------------------------------------- polynomial activation with norms
+// out[r, :] = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 over a row z of F values, powers element by element and
+// N(v) = v / sqrt(mean(v^2) + eps): three sums of the row (z^2, z^4, z^6) in fp32, then one pass.  `coef` holds the
+// four numbers on the device.
+template <typename TO>
+__global__ void polynorm_kernel(const float* __restrict__ z, const float* __restrict__ coef, TO* __restrict__ out, int F,
+                                float eps) {
+  __shared__ float part[3][32];
+  __shared__ float inv_s[3];
+  const int r = blockIdx.x;
+  const float* src = z + (size_t)r * F;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    const float v = src[i], v2 = v * v, v3 = v2 * v;
+    s1 = fmaf(v, v, s1);
+    s2 = fmaf(v2, v2, s2);
+    s3 = fmaf(v3, v3, s3);
+  }
+  s1 = warp_sum(s1);
+  s2 = warp_sum(s2);
+  s3 = warp_sum(s3);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) {
+    part[0][wid] = s1;
+    part[1][wid] = s2;
+    part[2][wid] = s3;
+  }
+  __syncthreads();
+  if (threadIdx.x < 3) {
+    float tot = 0.f;
+    for (int i = 0; i < nw; ++i) tot += part[threadIdx.x][i];
+    inv_s[threadIdx.x] = 1.0f / sqrtf(tot / (float)F + eps);
+  }
+  __syncthreads();
+  const float a = coef[0] * inv_s[0], b = coef[1] * inv_s[1], c = coef[2] * inv_s[2], e = coef[3];
+  TO* dst = out + (size_t)r * F;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    const float v = src[i], v2 = v * v;
+    dst[i] = from_f32<TO>(a * v + b * v2 + c * (v2 * v) + e);
+  }
+}
+
+HK_API int hk_polynorm(const float* z, const float* coef, void* out, int out_dtype, int n, int F, float eps, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = F >= 2048 ? 256 : 128;
+  if (out_dtype == HK_F32) return hk_launch(polynorm_kernel<float>, dim3((unsigned)n), dim3(threads), 0, s, z, coef, (float*)out, F, eps);
+  if (out_dtype == HK_BF16) return hk_launch(polynorm_kernel<bf16>, dim3((unsigned)n), dim3(threads), 0, s, z, coef, (bf16*)out, F, eps);
+  return HK_ERR_UNSUPPORTED;
+}
+
+// ----------------------------------------------------------------------------- tanh of some columns
+// out[t, j] = tanh(x[t * ld + j]) for j < R, narrowed to TO: the hidden layer of a low-rank projection that sits in
+// a slice of a fused projection's output.
+template <typename TO>
+__global__ void tanh_cols_kernel(const float* __restrict__ x, long long ld, TO* __restrict__ out, long long total, int R) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / R;
+  const int j = (int)(i % R);
+  out[i] = from_f32<TO>(tanhf(x[t * ld + j]));
+}
+
+HK_API int hk_tanh_cols(const float* x, long long ld, void* out, int out_dtype, int n, int R, void* stream) {
+  if (n <= 0 || R <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long total = (long long)n * R;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (out_dtype == HK_F32) return hk_launch(tanh_cols_kernel<float>, dim3(blocks), dim3(256), 0, s, x, ld, (float*)out, total, R);
+  if (out_dtype == HK_BF16) return hk_launch(tanh_cols_kernel<bf16>, dim3(blocks), dim3(256), 0, s, x, ld, (bf16*)out, total, R);
   return HK_ERR_UNSUPPORTED;
 }

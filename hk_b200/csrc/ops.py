@@ -201,23 +201,25 @@ PAIRINGS = {"half": 0, "adjacent": 1}
 
 def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_dim, positions,
                           slot_of_token, block_table, k_pages, v_pages, n_heads, n_kv_heads, head_dim,
-                          page_tokens, write_kv=True, bias=None, pairing="half") -> None:
+                          page_tokens, write_kv=True, bias=None, pairing="half", norm_after=False, tied_v=False) -> None:
     """Splits the fused projection qkv[n, (H+2G)*hd] (float32): q heads are normalised (if
     q_weight), rotated (if rotary_dim > 0) and stored to q_out[n, H*hd]; k heads likewise and
     stored, with the v heads, into the token's cache page [page, G, page_tokens, hd].
     `bias` (float32 [(H+2G)*hd]) is added to the projection first.  `pairing`: "half" rotates dims
-    (i, i + rotary_dim/2), "adjacent" dims (2i, 2i+1)."""
+    (i, i + rotary_dim/2), "adjacent" dims (2i, 2i+1).  `norm_after`: the per-head norm comes behind the
+    rotation, and a missing weight then means a weight of ones.  `tied_v`: qkv is [n, (H+G)*hd] and a token's
+    value is its key as projected (before norm and rotation), of which the first v_pages.shape[-1] dims are kept."""
     if pairing not in PAIRINGS:
         raise KernelError(f"qk_norm_rope_kv_write: pairing {pairing!r} is neither 'half' nor 'adjacent'")
     if bias is not None:
         _need(bias, "bias", torch.float32, 1)
-        if bias.shape[0] != (n_heads + 2 * n_kv_heads) * head_dim:
-            raise KernelError("qk_norm_rope_kv_write: bias must have (H + 2G) * head_dim entries")
+        if bias.shape[0] != (n_heads + (1 if tied_v else 2) * n_kv_heads) * head_dim:
+            raise KernelError("qk_norm_rope_kv_write: bias must have one entry per projected column")
     _need(qkv, "qkv", torch.float32, 2)
     _need(q_out, "q_out", dims=2)
     n = qkv.shape[0]
     H, G, hd = n_heads, n_kv_heads, head_dim
-    if qkv.shape[1] != (H + 2 * G) * hd or tuple(q_out.shape) != (n, H * hd):
+    if qkv.shape[1] != (H + (1 if tied_v else 2) * G) * hd or tuple(q_out.shape) != (n, H * hd):
         raise KernelError("qk_norm_rope_kv_write: qkv or q_out has the wrong shape")
     if head_dim > 256:
         raise KernelError(f"qk_norm_rope_kv_write: head_dim {head_dim} is above 256")
@@ -237,8 +239,10 @@ def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_
         _need(block_table, "block_table", torch.int32, 2)
         _need(k_pages, "k_pages", q_out.dtype, 4)
         _need(v_pages, "v_pages", q_out.dtype, 4)
-        if tuple(k_pages.shape[1:]) != (G, page_tokens, hd) or k_pages.shape != v_pages.shape:
+        if tuple(k_pages.shape[1:]) != (G, page_tokens, hd) or tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3]) \
+                or not 1 <= v_pages.shape[3] <= hd or (v_pages.shape[3] != hd and not tied_v):
             raise KernelError("cache pages must be [pages, G, page_tokens, head_dim]")
+    vd = int(v_pages.shape[3]) if write_kv else hd
     lib = build.load("elementwise")
     _check(lib.hk_qk_norm_rope_kv_write(
         _ptr(qkv), _ptr(q_out), _dt(q_out), _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps),
@@ -246,7 +250,7 @@ def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_
         _ptr(positions), _ptr(slot_of_token), _ptr(block_table if write_kv else None),
         int(block_table.shape[1]) if write_kv else 0, _ptr(k_pages if write_kv else None),
         _ptr(v_pages if write_kv else None), n, H, G, hd, int(page_tokens), 1 if write_kv else 0, _ptr(bias),
-        PAIRINGS[pairing], _stream()),
+        PAIRINGS[pairing], 1 if norm_after else 0, 1 if tied_v else 0, vd, _stream()),
         "qk_norm_rope_kv_write")
 
 
@@ -296,11 +300,13 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool =
 
 
 def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, out, n_heads, n_kv_heads,
-                    head_dim, page_tokens, window: int, scale: float, plan=None) -> None:
+                    head_dim, page_tokens, window: int, scale: float, plan=None, sink: bool = False) -> None:
     """out[t, h, :] = softmax_j(scale * q[t, h] . k[j]) v[j] over the keys j in
     [max(0, p - window + 1), p] (all of [0, p] when window <= 0) of the token's request, read
     through its block-table row; p = positions[t].  `plan` carries the per-request tiling the
-    flash kernel wants; without it (or for sizes it refuses) the generic kernel runs."""
+    flash kernel wants; without it (or for sizes it refuses) the generic kernel runs.  Values may be narrower than
+    keys (v_pages [pages, G, page_tokens, vd], out [n, H*vd]; generic kernel).  `sink`: one more term in the softmax's
+    denominator, a key of score 0 without a value: p_j = exp(s_j) / (1 + sum exp(s_j))."""
     _need(q, "q", dims=2)
     _need(out, "out", q.dtype, 2)
     _need(k_pages, "k_pages", q.dtype, 4)
@@ -310,19 +316,20 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
     _need(slot_of_token, "slot_of_token", torch.int32, 1)
     n = q.shape[0]
     H, G, hd = n_heads, n_kv_heads, head_dim
-    if tuple(q.shape) != (n, H * hd) or out.shape != q.shape:
-        raise KernelError("paged_attention: q and out must be [n, H*head_dim]")
-    if tuple(k_pages.shape[1:]) != (G, page_tokens, hd) or k_pages.shape != v_pages.shape:
+    vd = int(v_pages.shape[3])
+    if tuple(q.shape) != (n, H * hd) or tuple(out.shape) != (n, H * vd):
+        raise KernelError("paged_attention: q must be [n, H*head_dim] and out [n, H*value_dim]")
+    if tuple(k_pages.shape[1:]) != (G, page_tokens, hd) or tuple(k_pages.shape[:3]) != tuple(v_pages.shape[:3]) or not 1 <= vd <= hd:
         raise KernelError("paged_attention: cache pages must be [pages, G, page_tokens, head_dim]")
     if H % G != 0:
         raise KernelError(f"paged_attention: {H} heads are not a multiple of {G} groups")
     if hd > 256:
         raise KernelError(f"paged_attention: head_dim {hd} is above 256")
     choice = _forced["attention"]
-    if q.dtype == torch.bfloat16 and choice != "generic" and plan is not None:
+    if q.dtype == torch.bfloat16 and choice != "generic" and plan is not None and vd == hd:
         from . import attention_fast
         if attention_fast.run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan,
-                              allow_tma=choice != "flash_cp"):
+                              allow_tma=choice != "flash_cp", sink=sink):
             return
         if choice is not None:
             raise KernelError(f"paged_attention: the '{choice}' kernel refuses head_dim={hd} page_tokens={page_tokens}")
@@ -330,7 +337,7 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
     _check(lib.hk_attention_generic(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _dt(q), _ptr(block_table), int(block_table.shape[1]),
         _ptr(positions), _ptr(slot_of_token), _ptr(out), n, H, G, hd, int(page_tokens), int(window),
-        ctypes.c_float(scale), _stream()), "paged_attention")
+        ctypes.c_float(scale), vd, 1 if sink else 0, _stream()), "paged_attention")
 
 
 # ---- sampling -------------------------------------------------------------------------
@@ -379,3 +386,184 @@ def sample(logits, temperature, top_k, top_p, min_p, seeds, counters, out) -> No
     lib = build.load("sampling")
     _check(lib.hk_sample(_ptr(logits), rows, logits.shape[1], _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p),
                          _ptr(seeds), _ptr(counters), _ptr(out), _stream()), "sample")
+
+
+# ---- a layer that norms both sides of its sublayers --------------------------------------
+
+
+def rms_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor) -> None:
+    """residual[r, :] += y[r, :] * rsqrt(mean(y^2) + eps) * weight (all float32): the norm behind a sublayer, fused
+    with the residual sum."""
+    _need(y, "y", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    _need(residual, "residual", torch.float32, 2)
+    if y.shape != residual.shape or weight.shape[0] != y.shape[1]:
+        raise KernelError("rms_norm_add: y, residual and weight do not fit")
+    lib = build.load("elementwise")
+    _check(lib.hk_rms_norm_add(_ptr(y), _ptr(weight), _ptr(residual), y.shape[0], y.shape[1], ctypes.c_float(eps), _stream()),
+           "rms_norm_add")
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 per row, N(v) = v / sqrt(mean(v^2) + eps), powers element by
+    element; z float32 [n, F], coef float32 [4] on the device."""
+    _need(z, "z", torch.float32, 2)
+    _need(coef, "coef", torch.float32, 1)
+    _need(out, "out", dims=2)
+    if out.shape != z.shape or coef.shape[0] != 4:
+        raise KernelError("polynorm: out must have z's shape and coef four entries")
+    lib = build.load("elementwise")
+    _check(lib.hk_polynorm(_ptr(z), _ptr(coef), _ptr(out), _dt(out), z.shape[0], z.shape[1], ctypes.c_float(eps), _stream()),
+           "polynorm")
+
+
+def _cols(x: torch.Tensor, name: str, width: int) -> int:
+    """Checks a float32 column slice [n, width] of a row-major matrix; returns its row stride."""
+    if not isinstance(x, torch.Tensor) or not x.is_cuda or x.dtype != torch.float32 or x.dim() != 2:
+        raise KernelError(f"{name} must be a float32 CUDA matrix")
+    if x.shape[1] != width or x.stride(1) != 1:
+        raise KernelError(f"{name} must be [n, {width}] with unit column stride")
+    return int(x.stride(0))
+
+
+def tanh_cols(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = tanh(x) for a column slice x (float32, any row stride) of a fused projection's output."""
+    _need(out, "out", dims=2)
+    ld = _cols(x, "x", out.shape[1])
+    if x.shape[0] != out.shape[0]:
+        raise KernelError("tanh_cols: rows differ")
+    lib = build.load("elementwise")
+    _check(lib.hk_tanh_cols(_ptr(x), ctypes.c_longlong(ld), _ptr(out), _dt(out), out.shape[0], out.shape[1], _stream()), "tanh_cols")
+
+
+# ---- recurrent mixers ---------------------------------------------------------------------
+
+
+def delta_rule_scan(r, k, v, a_logit, w_logit, a_bias, w_bias, segments, state, out, n_heads: int, key_dim: int,
+                    value_dim: int, decay_scale: float, key_eps: float) -> None:
+    """Generalised delta rule over the rows of every segment (slot, first row, rows) of `segments` int32 [n_seg, 3]:
+        S <- diag(d) S - (a * u) (u^T S) + k v^T,  out = S^T r      per head, S = state[slot, head] float32 [dk, dv]
+    d = exp(-decay_scale * sigmoid(w_logit + w_bias)), a = sigmoid(a_logit + a_bias), u = k / sqrt(sum k^2 + key_eps).
+    r, k, a_logit [n, H*dk] and v [n, H*dv] are float32 column slices of ONE matrix (one row stride); w_logit is
+    float32 [n, H*dk] with its own.  out: float32 [n, H*dv]."""
+    H, dk, dv = n_heads, key_dim, value_dim
+    ld = _cols(r, "r", H * dk)
+    if _cols(k, "k", H * dk) != ld or _cols(a_logit, "a_logit", H * dk) != ld or _cols(v, "v", H * dv) != ld:
+        raise KernelError("delta_rule_scan: r, k, v and a_logit must be slices of one matrix")
+    ldw = _cols(w_logit, "w_logit", H * dk)
+    _need(a_bias, "a_bias", torch.float32, 1)
+    _need(w_bias, "w_bias", torch.float32, 1)
+    _need(segments, "segments", torch.int32, 2)
+    _need(state, "state", torch.float32, 4)
+    _need(out, "out", torch.float32, 2)
+    n = r.shape[0]
+    if tuple(state.shape[1:]) != (H, dk, dv) or tuple(out.shape) != (n, H * dv) or segments.shape[1] != 3 \
+            or a_bias.shape[0] != H * dk or w_bias.shape[0] != H * dk:
+        raise KernelError("delta_rule_scan: shapes do not fit")
+    lib = build.load("recurrent")
+    _check(lib.hk_delta_rule_scan(_ptr(r), _ptr(k), _ptr(v), _ptr(a_logit), ctypes.c_longlong(ld), _ptr(w_logit),
+                                  ctypes.c_longlong(ldw), _ptr(a_bias), _ptr(w_bias), _ptr(segments), int(segments.shape[0]),
+                                  _ptr(state), _ptr(out), H, dk, dv, ctypes.c_float(decay_scale), ctypes.c_float(key_eps),
+                                  _stream()), "delta_rule_scan")
+
+
+def head_norm_gate(o, gate_logit, weight, eps: float, out, n_heads: int, value_dim: int) -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h]^2) + eps) * weight[h, :] * sigmoid(gate_logit[t, h, :])."""
+    H, dv = n_heads, value_dim
+    _need(o, "o", torch.float32, 2)
+    ldg = _cols(gate_logit, "gate_logit", H * dv)
+    _need(weight, "weight", torch.float32, 1)
+    _need(out, "out", dims=2)
+    if tuple(o.shape) != (out.shape[0], H * dv) or out.shape != o.shape or weight.shape[0] != H * dv:
+        raise KernelError("head_norm_gate: shapes do not fit")
+    lib = build.load("recurrent")
+    _check(lib.hk_head_norm_gate(_ptr(o), _ptr(gate_logit), ctypes.c_longlong(ldg), _ptr(weight), _ptr(out), _dt(out),
+                                 o.shape[0], H, dv, ctypes.c_float(eps), _stream()), "head_norm_gate")
+
+
+def mingru_scan(proj, z_bias, x_bias, segments, state, out) -> None:
+    """minGRU over the rows of every segment: proj float32 [n, 3W] = [z logits | candidate inputs | gate inputs];
+    S <- (1 - z) S + z c, z = sigmoid(zl + z_bias), c = x + 1/2 (x >= 0) or sigmoid(x), x = xl + x_bias;
+    out = S * silu(gate input).  state float32 [slots, W]."""
+    _need(proj, "proj", torch.float32, 2)
+    _need(segments, "segments", torch.int32, 2)
+    _need(state, "state", torch.float32, 2)
+    _need(out, "out", dims=2)
+    W = state.shape[1]
+    for name, b in (("z_bias", z_bias), ("x_bias", x_bias)):
+        if b is not None:
+            _need(b, name, torch.float32, 1)
+            if b.shape[0] != W:
+                raise KernelError(f"mingru_scan: {name} must have one entry per channel")
+    if proj.shape[1] != 3 * W or tuple(out.shape) != (proj.shape[0], W) or segments.shape[1] != 3:
+        raise KernelError("mingru_scan: shapes do not fit")
+    lib = build.load("recurrent")
+    _check(lib.hk_mingru_scan(_ptr(proj), ctypes.c_longlong(3 * W), _ptr(z_bias), _ptr(x_bias), _ptr(segments),
+                              int(segments.shape[0]), _ptr(state), _ptr(out), _dt(out), W, _stream()), "mingru_scan")
+
+
+# ---- routed feed-forward -------------------------------------------------------------------
+
+
+def route_tile_rows() -> int:
+    """Rows per tile of the grouped products."""
+    return int(build.load("routed").hk_route_tile_rows())
+
+
+def route_topk(x, w_router, ids, weights) -> None:
+    """Per row of x [n, d]: the `top` = ids.shape[1] largest of the E float32 router logits x . w_router[e]
+    (w_router float32 [E, d]; the lower index wins a tie), and the softmax over the chosen logits."""
+    _need(x, "x", dims=2)
+    _need(w_router, "w_router", torch.float32, 2)
+    _need(ids, "ids", torch.int32, 2)
+    _need(weights, "weights", torch.float32, 2)
+    n, d = x.shape
+    if w_router.shape[1] != d or ids.shape[0] != n or ids.shape != weights.shape:
+        raise KernelError("route_topk: shapes do not fit")
+    lib = build.load("routed")
+    _check(lib.hk_route_topk(_ptr(x), _dt(x), _ptr(w_router), _ptr(ids), _ptr(weights), n, d, w_router.shape[0],
+                             ids.shape[1], _stream()), "route_topk")
+
+
+def route_sort(ids, n_experts: int, offsets, perm, inv, tiles) -> None:
+    """Lays the (row, choice) pairs out by expert: offsets int32 [E+1], perm [pairs] (sorted place -> pair), inv [pairs]
+    (pair -> sorted place), tiles int32 [max_tiles, 2] = (expert, first sorted place) of every tile of
+    `route_tile_rows()` rows, -1 for unused tiles."""
+    for name, t in (("ids", ids), ("offsets", offsets), ("perm", perm), ("inv", inv), ("tiles", tiles)):
+        _need(t, name, torch.int32)
+    pairs = ids.numel()
+    if offsets.numel() != n_experts + 1 or perm.numel() != pairs or inv.numel() != pairs or tiles.dim() != 2 or tiles.shape[1] != 2:
+        raise KernelError("route_sort: shapes do not fit")
+    lib = build.load("routed")
+    _check(lib.hk_route_sort(_ptr(ids), pairs, n_experts, _ptr(offsets), _ptr(perm), _ptr(inv), _ptr(tiles), tiles.shape[0],
+                             _stream()), "route_sort")
+
+
+def grouped_gemm(a, w, out, tiles, offsets, perm, top: int, gather: bool, gated: bool) -> None:
+    """A product per expert over the sorted rows.  w [E, N, K] (gated: [E, 2N, K] = N gate rows then N up rows);
+    row p of the product reads a[perm[p] // top] (gather) or a[p]; out[p, :N] = a . w[e]^T in float32, or
+    silu(gate) * up in a's type when gated."""
+    _need(a, "a", dims=2)
+    _need(w, "w", a.dtype, 3)
+    _need(out, "out", dims=2)
+    K = a.shape[1]
+    N = out.shape[1]
+    if w.shape[2] != K or w.shape[1] != (2 * N if gated else N) or out.dtype != (a.dtype if gated else torch.float32):
+        raise KernelError("grouped_gemm: shapes or types do not fit")
+    lib = build.load("routed")
+    _check(lib.hk_grouped_gemm(_ptr(a), _ptr(w), _dt(a), _ptr(out), _ptr(tiles), tiles.shape[0], _ptr(offsets), _ptr(perm),
+                               int(top), 1 if gather else 0, N, K, 1 if gated else 0, _stream()), "grouped_gemm")
+
+
+def route_combine(ys, inv, weights, y, accumulate: bool = False) -> None:
+    """y[t, :] (+)= sum_k weights[t, k] * ys[inv[t, k], :], the choices in their order (all float32)."""
+    _need(ys, "ys", torch.float32, 2)
+    _need(inv, "inv", torch.int32)
+    _need(weights, "weights", torch.float32, 2)
+    _need(y, "y", torch.float32, 2)
+    n, top = weights.shape
+    if y.shape[0] != n or ys.shape[1] != y.shape[1] or inv.numel() != n * top or ys.shape[0] != n * top:
+        raise KernelError("route_combine: shapes do not fit")
+    lib = build.load("routed")
+    _check(lib.hk_route_combine(_ptr(ys), _ptr(inv), _ptr(weights), _ptr(y), n, y.shape[1], top, 1 if accumulate else 0,
+                                _stream()), "route_combine")

@@ -1,0 +1,262 @@
+// A feed-forward of experts with a router: every token goes to `top` of `E` small feed-forwards.
+//
+// Everything that depends on the router's choice stays on the device, so the launches of a step depend
+// on its number of rows alone (a decode step through it can be captured in a graph):
+//   1. route:   one warp per token takes the E router logits (float32 products of the token's vector with
+//               the router's rows, summed in a fixed order), picks the `top` largest (the lower index wins a
+//               tie) and gives them the softmax over the chosen logits as weights.
+//   2. sort:    one CTA counts the (token, choice) pairs per expert, lays the experts' rows out one after
+//               the other (`perm`: sorted place -> pair, `inv`: pair -> sorted place) and cuts every
+//               expert's rows into tiles of RT_BM rows (`tiles`: expert and first row, -1 for unused).
+//   3. experts: a grouped product over those tiles: tile rows are gathered through `perm`, the weights are
+//               the tile's expert's; first gate and up with silu(gate) * up in the epilogue, then down.
+//               A row's result does not depend on its place in a tile: every output element is one chain of
+//               k = 0..K-1 (the FMA kernel) or a fixed tree (the tensor-core kernel).
+//   4. combine: y[t] = sum over the token's choices, in the order of the choices, of weight * expert output.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+#define RT_BM 64
+#define RT_BN 64
+#define RT_BK 16
+
+// ------------------------------------------------------------------------------------ 1. route
+template <typename T>
+__global__ void route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids,
+                                  float* __restrict__ weights, int n, int d, int E, int top) {
+  extern __shared__ float sm[];               // [warps][E]
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + wid;
+  if (t >= n) return;
+  float* z = sm + (size_t)wid * E;
+  const T* xr = x + (size_t)t * d;
+  for (int e = 0; e < E; ++e) {
+    const float* wr = w + (size_t)e * d;
+    float acc = 0.f;
+    for (int i = lane; i < d; i += 32) acc = fmaf(to_f32<T>(xr[i]), wr[i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncwarp();
+  float first = 0.f, mine = 0.f, total = 0.f;
+  int mine_id = 0;
+  for (int k = 0; k < top; ++k) {
+    float best = -CUDART_INF_F;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best) {                          // ascending e: the first maximum of this lane
+        best = v;
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (k == 0) first = best;
+    const float p = expf(best - first);        // the first chosen logit is the largest
+    total += p;
+    if (lane == (k & 31)) {                    // lane k keeps choice k (top <= 32)
+      mine = p;
+      mine_id = bi;
+    }
+    if (lane == 0 && bi < E) z[bi] = -CUDART_INF_F;
+    __syncwarp();
+  }
+  if (lane < top) {
+    ids[(size_t)t * top + lane] = mine_id < E ? mine_id : 0;
+    weights[(size_t)t * top + lane] = mine / total;
+  }
+}
+
+HK_API int hk_route_topk(const void* x, int dtype, const float* w, int* ids, float* weights, int n, int d, int E, int top,
+                         void* stream) {
+  if (n <= 0) return 0;
+  if (E < 1 || top < 1 || top > E || top > 32 || E > 2048) return HK_ERR_UNSUPPORTED;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * E * sizeof(float);
+  dim3 grid((unsigned)((n + warps - 1) / warps));
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == HK_F32)
+    return hk_launch(route_topk_kernel<float>, grid, dim3(warps * 32), smem, s, (const float*)x, w, ids, weights, n, d, E, top);
+  if (dtype == HK_BF16)
+    return hk_launch(route_topk_kernel<bf16>, grid, dim3(warps * 32), smem, s, (const bf16*)x, w, ids, weights, n, d, E, top);
+  return HK_ERR_UNSUPPORTED;
+}
+
+// ------------------------------------------------------------------------------------ 2. sort
+// offsets[E + 1], perm[pairs], inv[pairs], tiles[max_tiles][2].
+__global__ void __launch_bounds__(1024)
+route_sort_kernel(const int* __restrict__ ids, int pairs, int E, int bm, int* __restrict__ offsets, int* __restrict__ perm,
+                  int* __restrict__ inv, int* __restrict__ tiles, int max_tiles) {
+  extern __shared__ int smi[];                // counts[E], cursor[E]
+  int* counts = smi;
+  int* cursor = smi + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&counts[ids[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tile = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = at;
+      cursor[e] = at;
+      for (int r = 0; r < counts[e] && tile < max_tiles; r += bm) {
+        tiles[2 * tile] = e;
+        tiles[2 * tile + 1] = at + r;
+        ++tile;
+      }
+      at += counts[e];
+    }
+    offsets[E] = at;
+    for (; tile < max_tiles; ++tile) {
+      tiles[2 * tile] = -1;
+      tiles[2 * tile + 1] = 0;
+    }
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int at = atomicAdd(&cursor[ids[p]], 1);
+    perm[at] = p;
+    inv[p] = at;
+  }
+}
+
+HK_API int hk_route_sort(const int* ids, int pairs, int E, int* offsets, int* perm, int* inv, int* tiles, int max_tiles,
+                         void* stream) {
+  if (pairs <= 0) return 0;
+  if (E > 4096) return HK_ERR_UNSUPPORTED;
+  return hk_launch(route_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), (cudaStream_t)stream, ids, pairs, E,
+                   RT_BM, offsets, perm, inv, tiles, max_tiles);
+}
+
+HK_API int hk_route_tile_rows() { return RT_BM; }
+
+// ------------------------------------------------------------------------------------ 3. experts
+// out rows are sorted places.  GATED: w is [E][2N][K] = N gate rows then N up rows per expert, out[p, n] (type TO) =
+// silu(gate) * up.  Otherwise w is [E][N][K] and out[p, n] (float) = a[p] . w[e][n].  `gather`: row p of `a` is row
+// perm[p] / top of the tensor (the token's vector); else row p.
+template <typename T, typename TO, bool GATED>
+__global__ void __launch_bounds__(256)
+grouped_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, TO* __restrict__ out, const int* __restrict__ tiles,
+                    const int* __restrict__ offsets, const int* __restrict__ perm, int top, int gather, int N, int K) {
+  __shared__ float As[RT_BK][RT_BM + 4];
+  __shared__ float Ws[GATED ? 2 : 1][RT_BK][RT_BN + 4];
+  __shared__ int rows[RT_BM];
+  const int e = tiles[2 * blockIdx.y];
+  if (e < 0) return;
+  const int p0 = tiles[2 * blockIdx.y + 1];
+  const int p_end = min(p0 + RT_BM, offsets[e + 1]);
+  const int tid = threadIdx.x;
+  if (tid < RT_BM) {
+    const int p = p0 + tid;
+    rows[tid] = p < p_end ? (gather ? perm[p] / top : p) : -1;
+  }
+  __syncthreads();
+  const int n0 = blockIdx.x * RT_BN;
+  const int tx = tid & 15, ty = tid >> 4;
+  const T* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+  float acc[GATED ? 2 : 1][4][4];
+#pragma unroll
+  for (int s = 0; s < (GATED ? 2 : 1); ++s)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[s][i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += RT_BK) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = tid + j * 256;
+      const int r = i >> 4, c = i & 15;
+      const int gk = k0 + c, gn = n0 + r;
+      const int src = rows[r];
+      As[c][r] = (src >= 0 && gk < K) ? to_f32<T>(a[(size_t)src * K + gk]) : 0.f;
+      Ws[0][c][r] = (gn < N && gk < K) ? to_f32<T>(we[(size_t)gn * K + gk]) : 0.f;
+      if (GATED) Ws[GATED ? 1 : 0][c][r] = (gn < N && gk < K) ? to_f32<T>(we[(size_t)(N + gn) * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < RT_BK; ++kk) {
+      float av[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int s = 0; s < (GATED ? 2 : 1); ++s) {
+        float wv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wv[j] = Ws[s][kk][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[s][i][j] = fmaf(av[i], wv[j], acc[s][i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int p = p0 + ty * 4 + i;
+    if (p >= p_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn >= N) continue;
+      float val = acc[0][i][j];
+      if (GATED) {
+        const float u = acc[GATED ? 1 : 0][i][j];
+        val = val / (1.0f + expf(-val)) * u;
+      }
+      out[(size_t)p * N + gn] = from_f32<TO>(val);
+    }
+  }
+}
+
+HK_API int hk_grouped_gemm(const void* a, const void* w, int dtype, void* out, const int* tiles, int max_tiles, const int* offsets,
+                           const int* perm, int top, int gather, int N, int K, int gated, void* stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  if (max_tiles > 65535) return HK_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)((N + RT_BN - 1) / RT_BN), (unsigned)max_tiles);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == HK_F32) {
+    if (gated)
+      return hk_launch(grouped_gemm_kernel<float, float, true>, grid, dim3(256), 0, s, (const float*)a, (const float*)w, (float*)out,
+                       tiles, offsets, perm, top, gather, N, K);
+    return hk_launch(grouped_gemm_kernel<float, float, false>, grid, dim3(256), 0, s, (const float*)a, (const float*)w, (float*)out,
+                     tiles, offsets, perm, top, gather, N, K);
+  }
+  if (dtype == HK_BF16) {
+    if (gated)
+      return hk_launch(grouped_gemm_kernel<bf16, bf16, true>, grid, dim3(256), 0, s, (const bf16*)a, (const bf16*)w, (bf16*)out, tiles,
+                       offsets, perm, top, gather, N, K);
+    return hk_launch(grouped_gemm_kernel<bf16, float, false>, grid, dim3(256), 0, s, (const bf16*)a, (const bf16*)w, (float*)out, tiles,
+                     offsets, perm, top, gather, N, K);
+  }
+  return HK_ERR_UNSUPPORTED;
+}
+
+// ------------------------------------------------------------------------------------ 4. combine
+// y[t, :] (= or +=) sum_k weights[t, k] * ys[inv[t * top + k], :]
+__global__ void route_combine_kernel(const float* __restrict__ ys, const int* __restrict__ inv, const float* __restrict__ weights,
+                                     float* __restrict__ y, int d, int top, int accumulate) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(weights[(size_t)t * top + k], ys[(size_t)inv[(size_t)t * top + k] * d + i], acc);
+    float* o = y + (size_t)t * d + i;
+    *o = accumulate ? *o + acc : acc;
+  }
+}
+
+HK_API int hk_route_combine(const float* ys, const int* inv, const float* weights, float* y, int n, int d, int top, int accumulate,
+                            void* stream) {
+  if (n <= 0) return 0;
+  return hk_launch(route_combine_kernel, dim3((unsigned)n), dim3(d >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, ys, inv, weights,
+                   y, d, top, accumulate);
+}

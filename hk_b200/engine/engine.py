@@ -164,9 +164,9 @@ class Engine:
         self.max_context = int(max_context) if max_context else int(min(limit, max_tokens))
         self.max_batch_tokens = int(max_batch_tokens)
         # compile, side by side, the kernel libraries this precision runs on (and only those)
-        from ..csrc import build as _build
-        _build.build_many(_build.libraries_for(self.precision.compute == torch.bfloat16))
         self.model = build_model(config, self.max_context)
+        from ..csrc import build as _build
+        _build.build_many(_build.libraries_for(self.precision.compute == torch.bfloat16, self.model))
         specs = self.model.param_specs()
         with torch.no_grad():
             if random_seed is not None:

@@ -1,4 +1,4 @@
-from . import qwen3  # noqa: F401  (registers the architecture)
+from . import kedanex, qwen3  # noqa: F401  (register the architectures)
 from .spec import LayerCall, ModelSpec
 
 __all__ = ["LayerCall", "ModelSpec"]

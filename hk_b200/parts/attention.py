@@ -14,6 +14,15 @@ Sizes, the norm's eps, the position encoding (with its pairing of dims), the win
 biases on the projections are parameters.  The
 reference's attention has no window (src/engine/config.zig:271-279 refuses one); `window=w`
 limits the keys of position p to (p - w, p] and lets the cache give pages back.
+
+Further parameters, for designs other than the reference's:
+  `qk_norm_after` puts the per-head norm of q and k behind the rotation; `qk_norm_weight=False` makes it a norm
+  without a weight (x over its root mean square);
+  `value_from_key` drops the v projection: a token's value is its key as projected, before rotation and norm,
+  of which the first `v_head_dim` dims are kept (the cache then holds both forms of the key);
+  `sink` adds a term to the softmax's denominator, a key of score 0 that has no value:
+  p_j = exp(s_j) / (1 + sum exp(s_j));
+  `names` renames the tensors (keys q, k, v, o, q_norm, k_norm, and q_bias, k_bias, v_bias, o_bias).
 """
 from __future__ import annotations
 
@@ -33,7 +42,9 @@ class GQAAttention(Part):
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, prefix: str,
                  qk_norm_eps: Optional[float] = None, position: Optional[RotaryEmbedding] = None,
                  window: Optional[int] = None, scale: Optional[float] = None, qkv_bias: bool = False,
-                 o_bias: bool = False):
+                 o_bias: bool = False, qk_norm_after: bool = False, qk_norm_weight: bool = True,
+                 value_from_key: bool = False, v_head_dim: Optional[int] = None, sink: bool = False,
+                 names: Optional[Dict[str, str]] = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
         if head_dim > 256 or head_dim < 2:
@@ -41,6 +52,15 @@ class GQAAttention(Part):
         if position is not None and position.rotary_dim > head_dim:
             raise ValueError("the rotary width exceeds head_dim")
         self.hidden, self.H, self.G, self.hd = hidden, n_heads, n_kv_heads, head_dim
+        self.vd = head_dim if v_head_dim is None else int(v_head_dim)
+        if not 1 <= self.vd <= head_dim or (self.vd != head_dim and not value_from_key):
+            raise ValueError(f"value size {self.vd} must be head_dim, or at most head_dim when the values are the keys")
+        self.qk_norm_after, self.qk_norm_weight = bool(qk_norm_after), bool(qk_norm_weight)
+        self.value_from_key, self.sink = bool(value_from_key), bool(sink)
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "q_bias": "q_proj.bias",
+                      "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias"}
+        self.names.update(names or {})
         self.prefix = prefix
         self.qk_norm_eps = qk_norm_eps
         self.position = position
@@ -58,42 +78,45 @@ class GQAAttention(Part):
         return (self.position,) if self.position is not None else ()
 
     def own_param_specs(self) -> Dict[str, ParamSpec]:
-        p, H, G, hd, d = self.prefix, self.H, self.G, self.hd, self.hidden
+        p, H, G, hd, d, nm = self.prefix, self.H, self.G, self.hd, self.hidden, self.names
         specs = {
-            p + "q_proj.weight": ParamSpec((H * hd, d), MATRIX),
-            p + "k_proj.weight": ParamSpec((G * hd, d), MATRIX),
-            p + "v_proj.weight": ParamSpec((G * hd, d), MATRIX),
-            p + "o_proj.weight": ParamSpec((d, H * hd), MATRIX),
+            p + nm["q"]: ParamSpec((H * hd, d), MATRIX),
+            p + nm["k"]: ParamSpec((G * hd, d), MATRIX),
+            p + nm["o"]: ParamSpec((d, H * self.vd), MATRIX),
         }
-        if self.qk_norm_eps is not None:
-            specs[p + "q_norm.weight"] = ParamSpec((hd,), VECTOR, "one_plus_normal")
-            specs[p + "k_norm.weight"] = ParamSpec((hd,), VECTOR, "one_plus_normal")
+        if not self.value_from_key:
+            specs[p + nm["v"]] = ParamSpec((G * hd, d), MATRIX)
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
+            specs[p + nm["q_norm"]] = ParamSpec((hd,), VECTOR, "one_plus_normal")
+            specs[p + nm["k_norm"]] = ParamSpec((hd,), VECTOR, "one_plus_normal")
         if self.qkv_bias:
-            specs[p + "q_proj.bias"] = ParamSpec((H * hd,), VECTOR)
-            specs[p + "k_proj.bias"] = ParamSpec((G * hd,), VECTOR)
-            specs[p + "v_proj.bias"] = ParamSpec((G * hd,), VECTOR)
+            specs[p + nm["q_bias"]] = ParamSpec((H * hd,), VECTOR)
+            specs[p + nm["k_bias"]] = ParamSpec((G * hd,), VECTOR)
+            if not self.value_from_key:
+                specs[p + nm["v_bias"]] = ParamSpec((G * hd,), VECTOR)
         if self.o_bias:
-            specs[p + "o_proj.bias"] = ParamSpec((d,), VECTOR)
+            specs[p + nm["o_bias"]] = ParamSpec((d,), VECTOR)
         return specs
 
     def cache_spec(self):
-        return KVCacheSpec(self.G, self.hd, self.window)
+        return KVCacheSpec(self.G, self.hd, self.window, None if self.vd == self.hd else self.vd)
 
     def own_bind(self, tensors, precision: Precision) -> None:
-        p = self.prefix
-        qkv = [tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"], tensors[p + "v_proj.weight"]]
+        p, nm = self.prefix, self.names
+        parts = "qk" if self.value_from_key else "qkv"
+        qkv = [tensors[p + nm[c]] for c in parts]
         wide = torch.float32 if any(t.dtype == torch.float32 for t in qkv) else qkv[0].dtype    # one kept in 32-bit: all are
         self.w_qkv = torch.cat([t.to(wide) for t in qkv], dim=0).contiguous()
-        self.w_o = tensors[p + "o_proj.weight"]
+        self.w_o = tensors[p + nm["o"]]
         if self.qkv_bias:
-            self.b_qkv = torch.cat([tensors[p + f"{n}_proj.bias"] for n in "qkv"]).contiguous()
+            self.b_qkv = torch.cat([tensors[p + nm[c + "_bias"]] for c in parts]).contiguous()
         if self.o_bias:
-            self.b_o = tensors[p + "o_proj.bias"]
-        if self.qk_norm_eps is not None:
-            self.q_norm = tensors[p + "q_norm.weight"]
-            self.k_norm = tensors[p + "k_norm.weight"]
+            self.b_o = tensors[p + nm["o_bias"]]
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
+            self.q_norm = tensors[p + nm["q_norm"]]
+            self.k_norm = tensors[p + nm["k_norm"]]
         from ..csrc import attention_fast
-        if precision.compute == torch.bfloat16 and attention_fast.supported(self.hd, self.H // self.G):
+        if precision.compute == torch.bfloat16 and attention_fast.supported(self.hd, self.H // self.G) and self.vd == self.hd:
             self._tables_key = ("paged_attention_items", self.window or 0, self.H, self.G, self.hd)
             self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
 
@@ -138,11 +161,14 @@ class GQAAttention(Part):
         return attention_fast.plan_on_device(info, arrays["items"], arrays.get("merge"))
 
     # -- one step ------------------------------------------------------------------------
-    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True) -> None:
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
+                accumulate: bool = True) -> None:
+        """`accumulate=False` stores the mixer's result in `residual` instead of adding it (a block that norms the
+        result before the residual sum)."""
         n = xb.shape[0]
         H, G, hd = self.H, self.G, self.hd
         plan = self._plan(ctx) if xb.dtype == torch.bfloat16 else None
-        qkv = torch.empty((n, (H + 2 * G) * hd), dtype=torch.float32, device=xb.device)
+        qkv = torch.empty((n, self.w_qkv.shape[0]), dtype=torch.float32, device=xb.device)
         ops.gemm(xb, self.w_qkv, qkv)
         q = torch.empty((n, H * hd), dtype=xb.dtype, device=xb.device)
         cos = sin = None
@@ -155,12 +181,13 @@ class GQAAttention(Part):
         ops.qk_norm_rope_kv_write(
             qkv, q, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, cos, sin, rot, ctx.positions,
             ctx.slot_of_token, cache.block_table, cache.k_pages, cache.v_pages, H, G, hd, cache.page_tokens,
-            write_kv=write_cache, bias=self.b_qkv, pairing=pairing)
-        att = torch.empty_like(q)
+            write_kv=write_cache, bias=self.b_qkv, pairing=pairing, norm_after=self.qk_norm_after,
+            tied_v=self.value_from_key)
+        att = torch.empty((n, H * self.vd), dtype=xb.dtype, device=xb.device)
         ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.slot_of_token,
                             att, H, G, hd, cache.page_tokens, self.window or 0, self.scale,
-                            plan=plan)
-        ops.gemm(att, self.w_o, residual, accumulate=True, bias=self.b_o)
+                            plan=plan, sink=self.sink)
+        ops.gemm(att, self.w_o, residual, accumulate=accumulate, bias=self.b_o)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -32,3 +32,40 @@ class PreNormBlock(Part):
 
 
 register_part("block", "pre_norm", PreNormBlock)
+
+
+class SandwichNormBlock(Part):
+    """A layer that norms both sides of each sublayer:
+        x <- x + post_mixer_norm(mixer(mixer_norm(x)));   x <- x + post_ffn_norm(ffn(ffn_norm(x)))
+    The sublayer writes its float32 result into a buffer (`accumulate=False`); the norm behind it is fused with
+    the residual sum (`ops.rms_norm_add`).  Without a feed-forward (`feed_forward=None`) the second half is absent.
+    The norms are RMSNorm parts; their eps may differ."""
+    graph_safe = True   # reads the batch from device tensors only
+
+    def __init__(self, mixer_norm, mixer, post_mixer_norm, ffn_norm=None, feed_forward=None, post_ffn_norm=None):
+        if (feed_forward is None) != (ffn_norm is None) or (feed_forward is None) != (post_ffn_norm is None):
+            raise ValueError("a feed-forward comes with both of its norms, or none of the three is given")
+        self.mixer_norm, self.mixer, self.post_mixer_norm = mixer_norm, mixer, post_mixer_norm
+        self.ffn_norm, self.feed_forward, self.post_ffn_norm = ffn_norm, feed_forward, post_ffn_norm
+
+    def children(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.post_mixer_norm, self.ffn_norm, self.feed_forward,
+                                 self.post_ffn_norm) if p is not None)
+
+    def cache_specs(self):
+        return [self.mixer.cache_spec()]
+
+    def forward(self, residual: torch.Tensor, ctx, caches, write_cache: bool = True) -> None:
+        from ..csrc import ops
+        xb = torch.empty(residual.shape, dtype=ctx.precision.compute, device=residual.device)
+        y = torch.empty_like(residual)
+        self.mixer_norm.forward(residual, xb)
+        self.mixer.forward(xb, y, ctx, caches[0], write_cache, accumulate=False)
+        ops.rms_norm_add(y, self.post_mixer_norm.weight, self.post_mixer_norm.eps, residual)
+        if self.feed_forward is not None:
+            self.ffn_norm.forward(residual, xb)
+            self.feed_forward.forward(xb, y, ctx, accumulate=False)
+            ops.rms_norm_add(y, self.post_ffn_norm.weight, self.post_ffn_norm.eps, residual)
+
+
+register_part("block", "sandwich_norm", SandwichNormBlock)

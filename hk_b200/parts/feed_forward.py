@@ -9,7 +9,7 @@ from typing import Dict
 import torch
 
 from ..csrc import ops
-from .base import MATRIX, ParamSpec, Part, Precision, register_part
+from .base import MATRIX, VECTOR, ParamSpec, Part, Precision, register_part
 
 
 class SwiGLUFeedForward(Part):
@@ -38,10 +38,104 @@ class SwiGLUFeedForward(Part):
         self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[p + "down_proj.weight"]
 
-    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, accumulate: bool = True) -> None:
         h = torch.empty((xb.shape[0], self.F), dtype=xb.dtype, device=xb.device)
         ops.gemm_swiglu(xb, self.w_gate_up, h)
-        ops.gemm(h, self.w_down, residual, accumulate=True)
+        ops.gemm(h, self.w_down, residual, accumulate=accumulate)
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
+
+
+class PolyNormFeedForward(Part):
+    """residual += W_down act(W_up xb) with the polynomial activation
+        act(z) = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3,   N(v) = v / sqrt(mean(v^2) + eps) over a token's F values,
+    powers element by element; the four numbers are a tensor of the model (`act`).  The up product's result is
+    float32, the three means and the activation are computed in float32 and narrowed for the down product."""
+    graph_safe = True   # reads the batch from device tensors only
+
+    def __init__(self, hidden: int, intermediate: int, prefix: str, eps: float, names=None):
+        self.hidden, self.F, self.prefix, self.eps = hidden, intermediate, prefix, float(eps)
+        self.names = {"up": "up", "down": "down", "act": "act"}
+        self.names.update(names or {})
+        self.w_up = self.w_down = self.coef = None
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        p, nm = self.prefix, self.names
+        return {
+            p + nm["up"]: ParamSpec((self.F, self.hidden), MATRIX),
+            p + nm["down"]: ParamSpec((self.hidden, self.F), MATRIX),
+            p + nm["act"]: ParamSpec((4,), VECTOR, "one_plus_normal"),
+        }
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        p, nm = self.prefix, self.names
+        self.w_up, self.w_down, self.coef = tensors[p + nm["up"]], tensors[p + nm["down"]], tensors[p + nm["act"]]
+
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, accumulate: bool = True) -> None:
+        n = xb.shape[0]
+        z = torch.empty((n, self.F), dtype=torch.float32, device=xb.device)
+        ops.gemm(xb, self.w_up, z)
+        h = torch.empty((n, self.F), dtype=xb.dtype, device=xb.device)
+        ops.polynorm(z, self.coef, self.eps, h)
+        ops.gemm(h, self.w_down, residual, accumulate=accumulate)
+
+
+class RoutedFeedForward(Part):
+    """A mixture of `experts` SwiGLU feed-forwards of which every token uses `top`:
+        router logits z = W_router xb in float32; the `top` largest are chosen (the lower index wins a tie) and
+        weighted by the softmax over the chosen logits; residual += sum_k weight_k * W_down_e (silu(W_gate_e xb) * W_up_e xb).
+    The choice never leaves the device (`csrc/routed.cu`): tokens are sorted by expert there and the experts'
+    products run as one grouped product over tiles of the sorted rows, so the launches depend on the number of
+    rows alone.  The experts' weights are stacked at binding: [E, 2F, d] (gate rows, then up rows) and [E, d, F]."""
+    graph_safe = True   # reads the batch from device tensors only; launches depend on the row count alone
+    kernel_libraries = ("routed",)
+
+    def __init__(self, hidden: int, intermediate: int, n_experts: int, top: int, prefix: str, names=None):
+        if not 1 <= top <= n_experts or top > 32:
+            raise ValueError(f"top = {top} must be in 1..min(experts, 32) (experts = {n_experts})")
+        self.hidden, self.F, self.E, self.top, self.prefix = hidden, intermediate, n_experts, top, prefix
+        self.names = {"router": "router", "expert": "e{}.", "gate": "gate", "up": "up", "down": "down"}
+        self.names.update(names or {})
+        self.w_router = self.w_gate_up = self.w_down = None
+
+    def _expert(self, e: int, which: str) -> str:
+        return self.prefix + self.names["expert"].format(e) + self.names[which]
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        specs = {self.prefix + self.names["router"]: ParamSpec((self.E, self.hidden), MATRIX)}
+        for e in range(self.E):
+            specs[self._expert(e, "gate")] = ParamSpec((self.F, self.hidden), MATRIX)
+            specs[self._expert(e, "up")] = ParamSpec((self.F, self.hidden), MATRIX)
+            specs[self._expert(e, "down")] = ParamSpec((self.hidden, self.F), MATRIX)
+        return specs
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        self.w_router = tensors[self.prefix + self.names["router"]].float().contiguous()    # the router runs in 32-bit
+        dt = precision.compute
+        self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")].to(dt), tensors[self._expert(e, "up")].to(dt)])
+                                      for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down")].to(dt) for e in range(self.E)]).contiguous()
+        self._tile_rows = ops.route_tile_rows()
+
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, accumulate: bool = True) -> None:
+        n, dev = xb.shape[0], xb.device
+        pairs = n * self.top
+        ids = torch.empty((n, self.top), dtype=torch.int32, device=dev)
+        weights = torch.empty((n, self.top), dtype=torch.float32, device=dev)
+        ops.route_topk(xb, self.w_router, ids, weights)
+        max_tiles = pairs // self._tile_rows + min(self.E, pairs)
+        offsets = torch.empty(self.E + 1, dtype=torch.int32, device=dev)
+        perm = torch.empty(pairs, dtype=torch.int32, device=dev)
+        inv = torch.empty(pairs, dtype=torch.int32, device=dev)
+        tiles = torch.empty((max_tiles, 2), dtype=torch.int32, device=dev)
+        ops.route_sort(ids, self.E, offsets, perm, inv, tiles)
+        h = torch.empty((pairs, self.F), dtype=xb.dtype, device=dev)
+        ops.grouped_gemm(xb, self.w_gate_up, h, tiles, offsets, perm, self.top, gather=True, gated=True)
+        ys = torch.empty((pairs, self.hidden), dtype=torch.float32, device=dev)
+        ops.grouped_gemm(h, self.w_down, ys, tiles, offsets, perm, self.top, gather=False, gated=False)
+        ops.route_combine(ys, inv, weights, residual, accumulate=accumulate)
+
+
+register_part("feed_forward", "polynorm", PolyNormFeedForward)
+register_part("feed_forward", "routed_swiglu", RoutedFeedForward)

@@ -45,6 +45,11 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def _fits(found, declared) -> bool:
+    """A declared extent of -1 takes any size (a width that only the file knows)."""
+    return len(found) == len(declared) and all(d == -1 or int(f) == int(d) for f, d in zip(found, declared))
+
+
 def _skipped(name: str) -> bool:
     return name.endswith("rotary_emb.inv_freq")
 
@@ -64,9 +69,9 @@ def load_tensors(model_dir: str, specs: Dict[str, ParamSpec], precision: Precisi
         if name not in where:
             continue
         dt, shape, _, _ = where[name].entries[name]
-        if tuple(shape) != tuple(spec.shape):
+        if not _fits(shape, spec.shape):
             wrong_shape[name] = (tuple(shape), tuple(spec.shape))
-        tdt = where[name].tensor(name).dtype if tuple(shape) == tuple(spec.shape) else None
+        tdt = where[name].tensor(name).dtype if _fits(shape, spec.shape) else None
         if tdt is not None:
             ok = tdt in _INT_DTYPES if spec.kind == TABLE else tdt in _FLOAT_DTYPES
             if not ok:
@@ -101,6 +106,8 @@ def random_tensors(specs: Dict[str, ParamSpec], seed: int, std: float, norm_std:
     for name, spec in specs.items():
         if spec.optional:
             continue
+        if any(int(e) < 0 for e in spec.shape):
+            raise ValueError(f"tensor '{name}' has an extent that only a file can give; random weights need all sizes")
         if spec.kind == TABLE:
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
