@@ -53,10 +53,13 @@ def libraries_for(bfloat16: bool, model=None) -> List[str]:
     name in their `kernel_libraries` (a recurrent mixer's scans, a routed feed-forward's kernels)."""
     needed = ["elementwise", "gemm_generic", "attention_generic"]
     if bfloat16:
-        needed += ["gemm_smallm", "gemm_stream", "gemm_tc", "attention_flash", "attention_prefill_tc"]
+        needed += ["gemm_smallm", "gemm_stream", "gemm_tc"]
+        if model is None:
+            needed += ["attention_flash", "attention_prefill_tc"]
 
     def walk(part):
-        for name in getattr(part, "kernel_libraries", ()):
+        names = getattr(part, "kernel_libraries", ())
+        for name in (names(bfloat16) if callable(names) else names):
             if name not in needed:
                 needed.append(name)
         for c in part.children():

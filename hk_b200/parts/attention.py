@@ -74,6 +74,14 @@ class GQAAttention(Part):
         self._sm_count = 0
 
     # -- declaration ---------------------------------------------------------------------
+    def kernel_libraries(self, bfloat16: bool):
+        """The flash kernels are compiled only for a model one of whose attention parts can use them."""
+        from ..csrc import attention_fast
+        if not bfloat16 or self.vd != self.hd or not attention_fast.supported(self.hd, self.H // self.G):
+            return ()
+        return ("attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.hd, self.H // self.G) \
+            else ("attention_flash",)
+
     def children(self):
         return (self.position,) if self.position is not None else ()
 

@@ -29,7 +29,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
-    ap.add_argument("--max-requests", type=int, default=8)
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: the most requests live at any time")
     ap.add_argument("--page-tokens", type=int, default=16)
     args = ap.parse_args(argv)
     if args.max_tokens < 1:
