@@ -47,7 +47,7 @@ def tc_prefill_supported(hd: int, group: int) -> bool:
 
 def tc2_prefill_supported(hd: int, group: int, page_tokens: int) -> bool:
     """The tcgen05 kernel with two query tiles per CTA and K/V by TMA: the pages must be whole boxes of a 128-key tile."""
-    boxes = (page_tokens % 8 == 0 and 128 % page_tokens == 0) or (page_tokens > 0 and page_tokens % 128 == 0)
+    boxes = page_tokens > 0 and ((page_tokens % 8 == 0 and 128 % page_tokens == 0) or page_tokens % 128 == 0)
     return tc_prefill_supported(hd, group) and boxes
 
 
