@@ -90,6 +90,8 @@ class RoutedFeedForward(Part):
     rows alone.  The experts' weights are stacked at binding: [E, 2F, d] (gate rows, then up rows) and [E, d, F]."""
     graph_safe = True   # reads the batch from device tensors only; launches depend on the row count alone
     kernel_libraries = ("routed",)
+    route_log = None    # a list, when someone wants to see the choices: every eager forward appends a copy of its
+                        # chosen experts int32 [rows, top] (a replayed graph runs no Python and appends nothing)
 
     def __init__(self, hidden: int, intermediate: int, n_experts: int, top: int, prefix: str, names=None):
         if not 1 <= top <= n_experts or top > 32:
@@ -124,6 +126,8 @@ class RoutedFeedForward(Part):
         ids = torch.empty((n, self.top), dtype=torch.int32, device=dev)
         weights = torch.empty((n, self.top), dtype=torch.float32, device=dev)
         ops.route_topk(xb, self.w_router, ids, weights)
+        if RoutedFeedForward.route_log is not None:
+            RoutedFeedForward.route_log.append(ids.clone())
         max_tiles = pairs // self._tile_rows + min(self.E, pairs)
         offsets = torch.empty(self.E + 1, dtype=torch.int32, device=dev)
         perm = torch.empty(pairs, dtype=torch.int32, device=dev)

@@ -27,7 +27,12 @@ def gelu_tanh(z):
     return 0.5 * z * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
+round_inputs = None      # a function, to model an implementation that narrows the inputs of its matrix products
+
+
 def linear(x, w, b=None):
+    if round_inputs is not None:
+        x = round_inputs(x)
     y = x @ w.T
     return y if b is None else y + b
 
@@ -122,6 +127,8 @@ def window_sink_attention(h, w, p, m, eps, first_position=0):
         q = rotate_half(q, pos, rot["base"], rot["dims"])
         k = rotate_half(k, pos, rot["base"], rot["dims"])
     q, k = unit_rms(q, eps), unit_rms(k, eps)
+    if round_inputs is not None:       # a cache that stores narrowed keys and values, and narrowed queries
+        q, k, v = round_inputs(q), round_inputs(k), round_inputs(v)
     window = m["mask"]["size"]
     out = np.zeros((T, H, vdim))
     for i in range(T):
@@ -146,13 +153,15 @@ def polynorm_ff(h, w, p, eps):
     return linear(act, w[p + "down"])
 
 
-def routed_ff(h, w, p, experts, top):
+def routed_ff(h, w, p, experts, top, routes=None):
     """Each token goes to the `top` experts with the largest router logits (the lower index wins a tie); their
-    weights are the softmax over the chosen logits; expert: W_down (silu(W_gate h) * (W_up h))."""
+    weights are the softmax over the chosen logits; expert: W_down (silu(W_gate h) * (W_up h)).
+    `routes` [T, top], when given, replaces the choice (not the weights): to follow an implementation whose
+    rounding fell the other way in a close call."""
     logits = linear(h, w[p + "router"])
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
-        chosen = np.argsort(-logits[t], kind="stable")[:top]
+        chosen = np.argsort(-logits[t], kind="stable")[:top] if routes is None else np.asarray(routes[t])
         z = logits[t, chosen]
         pw = np.exp(z - z.max())
         pw /= pw.sum()
@@ -160,6 +169,16 @@ def routed_ff(h, w, p, experts, top):
             q = f"{p}e{e}."
             out[t] += pe * linear(silu(linear(h[t], w[q + "gate"])) * linear(h[t], w[q + "up"]), w[q + "down"])
     return out
+
+
+def router_margin(h, w, p, top):
+    """Per token: by how much the last chosen router logit exceeds the best one not chosen, relative to the largest
+    |logit| of the token (infinite when every expert is chosen).  A small margin is a close call: rounding may choose
+    otherwise, and then the output is another one altogether."""
+    z = np.sort(linear(h, w[p + "router"]), axis=1)[:, ::-1]
+    if top >= z.shape[1]:
+        return np.full(z.shape[0], np.inf)
+    return (z[:, top - 1] - z[:, top]) / np.maximum(np.abs(z).max(axis=1), 1e-30)
 
 
 # ---------------------------------------------------------------------------- the model
@@ -171,10 +190,15 @@ def layer_prefix(layers, i):
     return f"l{i if j is None else j}."
 
 
-def forward(cfg, w, ids, with_layers=False):
+def forward(cfg, w, ids, with_layers=False, with_margins=False, routes=None):
+    """Logits [T, vocab]; with_layers: also the residual stream after every layer run; with_margins: also, per
+    position, the smallest `router_margin` over the layers.  `routes`: for every routed feed-forward in running
+    order, the experts [T, top] to use instead of its own choice."""
+    routes = list(routes) if routes is not None else None
     eps = cfg["norm"]["eps"]
     x = w["embed"][np.asarray(ids)]
     seen = []
+    margins = np.full(len(ids), np.inf)
     for i, layer in enumerate(cfg["layers"]):
         p = layer_prefix(cfg["layers"], i)
         m = layer["mixer"]
@@ -194,8 +218,11 @@ def forward(cfg, w, ids, with_layers=False):
             if mlp["kind"] == "dense":
                 y = polynorm_ff(h, w, p + "mlp.", eps)
             else:
-                y = routed_ff(h, w, p + "mlp.", mlp["router"]["experts"], mlp["router"]["top"])
+                y = routed_ff(h, w, p + "mlp.", mlp["router"]["experts"], mlp["router"]["top"],
+                              routes.pop(0) if routes is not None else None)
+                margins = np.minimum(margins, router_margin(h, w, p + "mlp.", mlp["router"]["top"]))
             x = x + rms_norm(y, w[p + "norm2b"], eps)
         seen.append(x.copy())
     logits = linear(rms_norm(x, w["final.norm"], eps), w["head"])
-    return (logits, np.stack(seen)) if with_layers else logits
+    out = (logits,) + ((np.stack(seen),) if with_layers else ()) + ((margins,) if with_margins else ())
+    return out if len(out) > 1 else logits
