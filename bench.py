@@ -310,6 +310,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in `config`)")
     ap.add_argument("--prefill-reps", type=int, default=7)
     ap.add_argument("--quick", action="store_true", help="skip batch 64")
+    ap.add_argument("--design", default="", help="instead of the default workload: prefill and decode throughput of another "
+                    "model design (kedanex) beside the Qwen3 decoder at equal width and depth, and its kernels one by one")
+    ap.add_argument("--design-widths", default="2048,4096", help="model widths for --design, with commas between them")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -321,6 +324,10 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design:
+        from hk_b200 import design_bench
+        print(json.dumps(design_bench.run(args.design, args, peaks())))
+        return 0
     run(args)
     return 0
 

@@ -204,8 +204,7 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
     from . import gemm_fast, ops
     if not supported(hd, H // G) or plan is None:
         return False
-    if sink:            # the flash kernels have no sink term yet: the generic kernel takes the step
-        return False
+    sk = 1 if sink else 0
     lib = build.load("attention_flash")
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     rows = 16 * plan.nw
@@ -214,7 +213,7 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
         part_o = torch.empty((plan.n_parts, G, rows, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((plan.n_parts, G, rows, 2), dtype=torch.float32, device=q.device)
     if plan.nw == 16:
-        if plan.n_parts or not tc2_prefill_supported(hd, H // G, int(page_tokens)):
+        if sink or plan.n_parts or not tc2_prefill_supported(hd, H // G, int(page_tokens)):
             return False
         lib_tc = build.load("attention_prefill_tc")
         code = lib_tc.hk_attention_prefill_tc2(
@@ -227,7 +226,7 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
         ops._check(code, "paged_attention (tcgen05 prefill, two query tiles)")
         return True
     if plan.nw == 8:
-        if plan.n_parts or not tc_prefill_supported(hd, H // G):
+        if sink or plan.n_parts or not tc_prefill_supported(hd, H // G):
             return False
         lib_tc = build.load("attention_prefill_tc")
         code = lib_tc.hk_attention_prefill_tc(
@@ -243,18 +242,18 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
         code = lib.hk_attention_decode_tma(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), ctypes.c_longlong(k_pages.shape[0]), _ptr(block_table),
             int(block_table.shape[1]), _ptr(plan.items), plan.n_items, _ptr(out), _ptr(part_o), _ptr(part_ml), H, G, hd,
-            int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)), plan.max_keys // int(page_tokens) + 2,
+            int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)), sk, plan.max_keys // int(page_tokens) + 2,
             _ptr(gemm_fast.status_flag(q.device)), stream)
     if code == _UNSUPPORTED:
         code = lib.hk_attention_flash(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), int(block_table.shape[1]),
                                       _ptr(plan.items), plan.n_items, plan.nw, _ptr(out), _ptr(part_o), _ptr(part_ml), H, G, hd,
-                                      int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)),
+                                      int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)), sk,
                                       plan.max_keys // int(page_tokens) + 2, stream)
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "paged_attention (flash)")
     if plan.n_parts:
         code = lib.hk_attention_combine(_ptr(part_o), _ptr(part_ml), _ptr(plan.first), _ptr(plan.count), _ptr(plan.row0),
-                                        _ptr(out), q.shape[0], H, G, hd, rows, stream)
+                                        _ptr(out), q.shape[0], H, G, hd, rows, sk, stream)
         ops._check(code, "paged_attention (combine)")
     return True

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(NW * 32, 3)
 attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                        const int* __restrict__ block_table, int table_stride, const Item* __restrict__ items,
                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G,
-                       int page_tokens, int window, float scale_log2) {
+                       int page_tokens, int window, float scale_log2, int sink) {
   constexpr int ROWS = NW * 16;
   constexpr int LD = HD + 8;            // padded row: (HD/8 + 1) 16-byte chunks, an odd count -> no ldmatrix conflicts
   constexpr int CPR = HD / 8;           // 16-byte chunks per row
@@ -262,7 +262,9 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
       if (!valid[i]) continue;
       const int tq = row[i] / group;
       bf16* op = out + ((size_t)(it.q_row0 + tq) * H + g * group + row[i] % group) * HD;
-      const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+      // a sink adds exp(0 - max) to the denominator: a key of score 0 that has no value
+      const float lt = l[i] + ((sink && m[i] > -CUDART_INF_F) ? exp2f(-m[i]) : 0.f);
+      const float inv = lt > 0.f ? 1.0f / lt : 0.f;
 #pragma unroll
       for (int n = 0; n < HD / 8; ++n)
         *reinterpret_cast<uint32_t*>(op + n * 8 + 2 * qt) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
@@ -295,7 +297,7 @@ __global__ void __launch_bounds__(DW * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int table_stride, const Item* __restrict__ items,
                         bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G,
-                        int page_tokens, int window, float scale_log2, int pages_cap) {
+                        int page_tokens, int window, float scale_log2, int sink, int pages_cap) {
   constexpr int ROWS = 16;
   constexpr int LD = HD + 8, CPR = HD / 8, KSTEPS = HD / 16;
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -477,6 +479,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     }
     if (it.part < 0) {
       const int tq = r / group;
+      if (sink && mx > -CUDART_INF_F) lsum += exp2f(-mx);
       if (tq < it.n_tokens)
         out[((size_t)(it.q_row0 + tq) * H + g * group + r % group) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
     } else {
@@ -540,7 +543,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const bf16* __restrict__ q, const int* __restrict__ block_table, int table_stride,
                             const Item* __restrict__ items, bf16* __restrict__ out, float* __restrict__ part_o,
                             float* __restrict__ part_ml, int H, int G, int page_tokens, int box_rows, int window,
-                            float scale_log2, int pages_cap, int* __restrict__ status) {
+                            float scale_log2, int sink, int pages_cap, int* __restrict__ status) {
   constexpr int ROWS = 16;
   constexpr int KSTEPS = HD / 16;
   constexpr int TILE_BYTES = TT * HD * 2;            // K (or V) of one stage
@@ -769,6 +772,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
     if (it.part < 0) {
       const int tq = r / group;
+      if (sink && mx > -CUDART_INF_F) lsum += exp2f(-mx);
       if (tq < it.n_tokens)
         out[((size_t)(it.q_row0 + tq) * H + g * group + r % group) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
     } else {
@@ -786,7 +790,7 @@ template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const int* __restrict__ first, const int* __restrict__ count,
                                          const int* __restrict__ row0, bf16* __restrict__ out, int n_tokens, int H, int G,
-                                         int rows) {
+                                         int rows, int sink) {
   pdl_launch_dependents();
   pdl_wait();
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -832,6 +836,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     }
   }
   lsum = warp_sum(lsum);
+  if (sink && mm > -CUDART_INF_F) lsum += exp2f(-mm);
   const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
   bf16* op = out + ((size_t)t * H + h) * HD;
 #pragma unroll
@@ -843,20 +848,20 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 
 template <int HD, int NW>
 int launch_flash(const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
-                 void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, cudaStream_t s) {
+                 void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int sink, cudaStream_t s) {
   const size_t smem = (size_t)4 * TILE_N * (HD + 8) * sizeof(bf16) + 2 * TILE_N * sizeof(int);
   static HkSmemCache allowed = {};
   if (int e = hk_allow_smem(attention_flash_kernel<HD, NW>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items * (unsigned)G);
   attention_flash_kernel<HD, NW><<<grid, NW * 32, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                             (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, window,
-                                                            scale_log2);
+                                                            scale_log2, sink);
   return hk_launch_status();
 }
 
 template <int HD>
 int launch_decode(const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
-                  void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int pages_cap,
+                  void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int sink, int pages_cap,
                   cudaStream_t s) {
   const size_t tiles = (size_t)2 * DS * DT * (HD + 8) * sizeof(bf16);
   const size_t merge = (size_t)DW * 16 * (HD + 2) * sizeof(float);
@@ -867,16 +872,16 @@ int launch_decode(const void* q, const void* kp, const void* vp, const int* bt, 
   dim3 grid((unsigned)n_items, (unsigned)G);
   attention_decode_kernel<HD><<<grid, DW * 32, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                          (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, window,
-                                                         scale_log2, pages_cap);
+                                                         scale_log2, sink, pages_cap);
   return hk_launch_status();
 }
 
 template <int HD>
 int launch_hd(int nw, const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
-              void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int pages_cap,
+              void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int sink, int pages_cap,
               cudaStream_t s) {
-  if (nw == 1) return launch_decode<HD>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, pages_cap, s);
-  if (nw == 4) return launch_flash<HD, 4>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, s);
+  if (nw == 1) return launch_decode<HD>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, sink, pages_cap, s);
+  if (nw == 4) return launch_flash<HD, 4>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, sink, s);
   return HK_ERR_UNSUPPORTED;
 }
 
@@ -889,26 +894,26 @@ int launch_hd(int nw, const void* q, const void* kp, const void* vp, const int* 
 // range spans (the decode variant keeps that many page ids in shared memory).
 HK_API int hk_attention_flash(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                               int table_stride, const void* items, int n_items, int nw, void* out, float* part_o,
-                              float* part_ml, int H, int G, int hd, int page_tokens, int window, float scale_log2,
+                              float* part_ml, int H, int G, int hd, int page_tokens, int window, float scale_log2, int sink,
                               int pages_cap, void* stream) {
   if (n_items <= 0) return 0;
   if (G < 1 || H % G != 0 || (H / G) > 16 * nw || G > 65535) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
 #define HK_HD(D) \
-  if (hd == D) return launch_hd<D>(nw, q, k_pages, v_pages, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens, window, scale_log2, pages_cap, s);
+  if (hd == D) return launch_hd<D>(nw, q, k_pages, v_pages, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens, window, scale_log2, sink, pages_cap, s);
   HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
 #undef HK_HD
   return HK_ERR_UNSUPPORTED;
 }
 
 HK_API int hk_attention_combine(const float* part_o, const float* part_ml, const int* first, const int* count,
-                                const int* row0, void* out, int n_tokens, int H, int G, int hd, int rows, void* stream) {
+                                const int* row0, void* out, int n_tokens, int H, int G, int hd, int rows, int sink, void* stream) {
   if (n_tokens <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int warps = 4;
   const unsigned grid = (unsigned)(((long long)n_tokens * H + warps - 1) / warps);
 #define HK_HD(D) \
-  if (hd == D) return hk_launch(attention_combine_kernel<D>, dim3(grid), dim3(warps * 32), 0, s, part_o, part_ml, first, count, row0, (bf16*)out, n_tokens, H, G, rows);
+  if (hd == D) return hk_launch(attention_combine_kernel<D>, dim3(grid), dim3(warps * 32), 0, s, part_o, part_ml, first, count, row0, (bf16*)out, n_tokens, H, G, rows, sink);
   HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
 #undef HK_HD
   return HK_ERR_UNSUPPORTED;
@@ -950,14 +955,14 @@ bool make_page_map(CUtensorMap* map, const void* ptr, unsigned long long rows, i
 template <int HD>
 int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int* bt, int stride, const void* items,
                       int n_items, void* out, float* part_o, float* part_ml, int H, int G, int pt, int box_rows, int window,
-                      float scale_log2, int pages_cap, int* status, cudaStream_t s) {
+                      float scale_log2, int sink, int pages_cap, int* status, cudaStream_t s) {
   const size_t smem = 1024 + (size_t)2 * TS * TT * HD * 2 + 2 * TS * sizeof(uint64_t) + 8 + (size_t)pages_cap * sizeof(int);
   if (smem > 110 * 1024) return HK_ERR_UNSUPPORTED;
   static HkSmemCache allowed = {};
   if (int e = hk_allow_smem(attention_decode_tma_kernel<HD>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items, (unsigned)G);
   return hk_launch_pdl(attention_decode_tma_kernel<HD>, grid, dim3((TW + 1) * 32), smem, s, mk, mv, (const bf16*)q, bt, stride,
-                       (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, box_rows, window, scale_log2, pages_cap, status);
+                       (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, box_rows, window, scale_log2, sink, pages_cap, status);
 }
 
 }  // namespace
@@ -968,7 +973,7 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
 HK_API int hk_attention_decode_tma(const void* q, const void* k_pages, const void* v_pages, long long num_pages,
                                    const int* block_table, int table_stride, const void* items, int n_items, void* out,
                                    float* part_o, float* part_ml, int H, int G, int hd, int page_tokens, int window,
-                                   float scale_log2, int pages_cap, int* status, void* stream) {
+                                   float scale_log2, int sink, int pages_cap, int* status, void* stream) {
   if (n_items <= 0) return 0;
   if (G < 1 || H % G != 0 || (H / G) > 16 || G > 65535) return HK_ERR_UNSUPPORTED;
   if ((hd != 64 && hd != 128) || page_tokens < 16 || (page_tokens & (page_tokens - 1))) return HK_ERR_UNSUPPORTED;
@@ -980,9 +985,9 @@ HK_API int hk_attention_decode_tma(const void* q, const void* k_pages, const voi
   cudaStream_t s = (cudaStream_t)stream;
   if (hd == 64)
     return launch_decode_tma<64>(mk, mv, q, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens,
-                                 box_rows, window, scale_log2, pages_cap, status, s);
+                                 box_rows, window, scale_log2, sink, pages_cap, status, s);
   return launch_decode_tma<128>(mk, mv, q, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens,
-                                box_rows, window, scale_log2, pages_cap, status, s);
+                                box_rows, window, scale_log2, sink, pages_cap, status, s);
 }
 
 // ---- the entry point that allocates nothing (see attention_noalloc.h) -------------------------------------
@@ -1027,7 +1032,7 @@ HK_API int hk_attention_decode_noalloc(const void* q, const void* k_pages, const
   float* part_o = scratch;
   float* part_ml = scratch + (size_t)n_parts * G * rows * hd;
   int code = hk_attention_flash(q, k_pages, v_pages, block_table, table_stride, items, n_items, 1, out, part_o, part_ml, H, G,
-                                hd, page_tokens, window, scale_log2, pages_cap, stream);
+                                hd, page_tokens, window, scale_log2, 0, pages_cap, stream);
   if (code != 0 || n_parts == 0) return code;
-  return hk_attention_combine(part_o, part_ml, first, count, row0, out, n_tokens, H, G, hd, (int)rows, stream);
+  return hk_attention_combine(part_o, part_ml, first, count, row0, out, n_tokens, H, G, hd, (int)rows, 0, stream);
 }

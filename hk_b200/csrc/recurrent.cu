@@ -11,8 +11,8 @@
 //     with the decay d_t = exp(-decay_scale * sigmoid(wl_t + w0)), the removal rate a_t = sigmoid(al_t + a0) and
 //     the unit key u_t = k_t / sqrt(sum(k_t^2) + key_eps).  The columns of S (one per value channel) never mix:
 //     a thread group owns one column, its dk entries spread over L lanes in registers, so a token costs two
-//     dot products over dk and no synchronisation.  What a token brings (d, a*u, u, k, r, v) is prepared for a
-//     chunk of tokens at a time in shared memory.
+//     dot products over dk and no synchronisation.  What a token brings (d, a*u, u, k, r, v) is prepared for all
+//     tokens at once by a kernel of its own and reaches the scan in chunks through shared memory.
 //   * gate of the delta rule's output: each head's o over its root mean square, times a weight, times
 //     sigmoid(g), narrowed to the compute type for the output projection.
 //   * minGRU (one scalar state per channel): S_t = (1 - z_t) S_(t-1) + z_t c_t with z_t = sigmoid(zl_t + bz),
@@ -23,28 +23,110 @@
 
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
+// ------------------------------------------------------------------ generalised delta rule: what a token brings
+// One warp per (token, head) writes the record [d | a*u | u | k | r | v] (5 dk + dv floats) that the scan reads:
+// everything that does not depend on the state is computed here, for all tokens at once.
+__global__ void delta_rule_prep_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
+                                       const float* __restrict__ al, long long ld, const float* __restrict__ wl, long long ldw,
+                                       const float* __restrict__ a_bias, const float* __restrict__ w_bias, float* __restrict__ rec,
+                                       long long items, int H, int dk, int dv, float decay_scale, float key_eps) {
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const size_t row = (size_t)(item / H);
+  const int h = (int)(item % H);
+  const size_t hoff = (size_t)h * dk;
+  const float* kp = k + row * ld + hoff;
+  float ss = 0.f;
+  for (int i = lane; i < dk; i += 32) {
+    const float kv = kp[i];
+    ss = fmaf(kv, kv, ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss + key_eps);
+  float* out = rec + (size_t)item * (5 * dk + dv);
+  for (int i = lane; i < dk; i += 32) {
+    const float kv = kp[i];
+    const float u = kv * inv;
+    const float a = sigmoid_f(al[row * ld + hoff + i] + a_bias[hoff + i]);
+    out[i] = expf(-decay_scale * sigmoid_f(wl[row * ldw + hoff + i] + w_bias[hoff + i]));
+    out[dk + i] = a * u;
+    out[2 * dk + i] = u;
+    out[3 * dk + i] = kv;
+    out[4 * dk + i] = r[row * ld + hoff + i];
+  }
+  for (int c = lane; c < dv; c += 32) out[5 * dk + c] = v[row * ld + (size_t)h * dv + c];
+}
+
 // ------------------------------------------------------------------ generalised delta rule: the scan
+// A block owns `cols` columns of one head's state for one segment.  Records arrive in chunks of `chunk` tokens through
+// a two-stage cp.async ring (the next chunk is on its way while this one is walked).  Per token the chain that the next
+// token waits for is: u . S (registers, two partial sums, L lanes by shuffle), then one fused update per state entry;
+// the output's dot product hangs off that chain.  With at most 8 state rows per thread the next token's vectors are
+// read into registers while this token's arithmetic runs.
 #define DR_MAX_RPT 32   // state rows a thread holds at most: dk <= 32 * L, L <= 32
 
+__device__ __forceinline__ void dr_cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
 template <int RPT>
-__global__ void delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
-                                       const float* __restrict__ al, long long ld, const float* __restrict__ wl, long long ldw,
-                                       const float* __restrict__ a_bias, const float* __restrict__ w_bias,
-                                       const int* __restrict__ segs, float* __restrict__ state, float* __restrict__ out,
-                                       int H, int dk, int dv, int L, int cols, int chunk, float decay_scale, float key_eps) {
-  extern __shared__ float sm[];
-  float* s_dec = sm;                          // [chunk][dk]
-  float* s_au = s_dec + (size_t)chunk * dk;
-  float* s_u = s_au + (size_t)chunk * dk;
-  float* s_k = s_u + (size_t)chunk * dk;
-  float* s_r = s_k + (size_t)chunk * dk;
-  float* s_v = s_r + (size_t)chunk * dk;      // [chunk][cols]
+struct DrToken {
+  float d[RPT], au[RPT], u[RPT], k[RPT], r[RPT], v;
+};
+
+template <int RPT>
+__device__ __forceinline__ void dr_read(DrToken<RPT>& t, const float* rec, int dk, int sub, int L, int vcol) {
+#pragma unroll
+  for (int m = 0; m < RPT; ++m) {
+    const int i = sub + L * m;
+    const bool ok = i < dk;
+    t.d[m] = ok ? rec[i] : 0.f;
+    t.au[m] = ok ? rec[dk + i] : 0.f;
+    t.u[m] = ok ? rec[2 * dk + i] : 0.f;
+    t.k[m] = ok ? rec[3 * dk + i] : 0.f;
+    t.r[m] = ok ? rec[4 * dk + i] : 0.f;
+  }
+  t.v = rec[5 * dk + vcol];
+}
+
+template <int RPT>
+__device__ __forceinline__ float dr_step(const DrToken<RPT>& t, float (&S)[RPT], int L) {
+  float du0 = 0.f, du1 = 0.f;
+#pragma unroll
+  for (int m = 0; m < RPT; m += 2) {
+    du0 = fmaf(t.u[m], S[m], du0);
+    if (m + 1 < RPT) du1 = fmaf(t.u[m + 1], S[m + 1], du1);
+  }
+  float du = du0 + du1;
+  for (int o = L >> 1; o > 0; o >>= 1) du += __shfl_xor_sync(0xffffffffu, du, o);
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+  for (int m = 0; m < RPT; m += 2) {
+    S[m] = fmaf(t.k[m], t.v, fmaf(-t.au[m], du, t.d[m] * S[m]));
+    a0 = fmaf(t.r[m], S[m], a0);
+    if (m + 1 < RPT) {
+      S[m + 1] = fmaf(t.k[m + 1], t.v, fmaf(-t.au[m + 1], du, t.d[m + 1] * S[m + 1]));
+      a1 = fmaf(t.r[m + 1], S[m + 1], a1);
+    }
+  }
+  float acc = a0 + a1;
+  for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  return acc;
+}
+
+template <int RPT>
+__global__ void delta_rule_scan_kernel(const float* __restrict__ rec, const int* __restrict__ segs, float* __restrict__ state,
+                                       float* __restrict__ out, int H, int dk, int dv, int L, int cols, int chunk) {
+  extern __shared__ __align__(16) float sm[];   // [2][chunk][5 dk + dv]
+  const int R = 5 * dk + dv;
   const int seg = blockIdx.x / H, h = blockIdx.x % H;
   const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
   const int col0 = blockIdx.y * cols;
-  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
-  const int sub = tid % L, col = col0 + tid / L;
-  const bool col_ok = tid / L < cols && col < dv;
+  const int tid = threadIdx.x;
+  const int sub = tid % L, cidx = tid / L, col = col0 + cidx;
+  const bool col_ok = cidx < cols && col < dv;
+  const int vcol = min(col, dv - 1);
   float S[RPT];
   float* sp = state + ((size_t)slot * H + h) * dk * dv;
 #pragma unroll
@@ -52,56 +134,60 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ r, const float*
     const int i = sub + L * m;
     S[m] = (col_ok && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
   }
-  const size_t hoff = (size_t)h * dk;
-  for (int t0 = 0; t0 < count; t0 += chunk) {
-    const int tc = min(chunk, count - t0);
-    __syncthreads();                          // the chunk before is consumed
-    for (int t = wid; t < tc; t += nw) {      // a warp prepares a token
-      const size_t row = (size_t)(row0 + t0 + t);
-      float ss = 0.f;
-      for (int i = lane; i < dk; i += 32) {
-        const float kv = k[row * ld + hoff + i];
-        ss = fmaf(kv, kv, ss);
+  const bool vec = (R & 3) == 0;                // records are whole 16-byte pieces (the base is 16-byte aligned)
+  auto fetch = [&](int c) {                     // chunk c -> stage c & 1
+    const int t0 = c * chunk, tc = min(chunk, count - t0);
+    float* dst = sm + (size_t)(c & 1) * chunk * R;
+    if (vec) {
+      const int pieces = R >> 2;
+      for (int i = tid; i < tc * pieces; i += blockDim.x) {
+        const int t = i / pieces, p = i % pieces;
+        dr_cp_async16(dst + (size_t)t * R + 4 * p, rec + ((size_t)(row0 + t0 + t) * H + h) * R + 4 * p);
       }
-      ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss + key_eps);
-      for (int i = lane; i < dk; i += 32) {
-        const float kv = k[row * ld + hoff + i];
-        const float u = kv * inv;
-        const float a = sigmoid_f(al[row * ld + hoff + i] + a_bias[hoff + i]);
-        const float d = expf(-decay_scale * sigmoid_f(wl[row * ldw + hoff + i] + w_bias[hoff + i]));
-        s_dec[t * dk + i] = d;
-        s_au[t * dk + i] = a * u;
-        s_u[t * dk + i] = u;
-        s_k[t * dk + i] = kv;
-        s_r[t * dk + i] = r[row * ld + hoff + i];
+    } else {
+      for (int i = tid; i < tc * R; i += blockDim.x) {
+        const int t = i / R, p = i % R;
+        dst[(size_t)t * R + p] = rec[((size_t)(row0 + t0 + t) * H + h) * R + p];
       }
-      for (int c = lane; c < cols; c += 32) s_v[t * cols + c] = col0 + c < dv ? v[row * ld + (size_t)h * dv + col0 + c] : 0.f;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int nchunks = (count + chunk - 1) / chunk;
+  float* op = out + (size_t)row0 * H * dv + (size_t)h * dv + col;
+  const bool writer = col_ok && sub == 0;
+  fetch(0);
+  for (int c = 0; c < nchunks; ++c) {
+    if (c + 1 < nchunks) {
+      fetch(c + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    for (int t = 0; t < tc; ++t) {
-      const float* pu = s_u + t * dk;
-      float du = 0.f;
-#pragma unroll
-      for (int m = 0; m < RPT; ++m) {
-        const int i = sub + L * m;
-        if (i < dk) du = fmaf(pu[i], S[m], du);
-      }
-      for (int o = L >> 1; o > 0; o >>= 1) du += __shfl_xor_sync(0xffffffffu, du, o);
-      const float vj = s_v[t * cols + min(tid / L, cols - 1)];
-      float acc = 0.f;
-#pragma unroll
-      for (int m = 0; m < RPT; ++m) {
-        const int i = sub + L * m;
-        if (i < dk) {
-          const float sn = fmaf(s_k[t * dk + i], vj, fmaf(-s_au[t * dk + i], du, s_dec[t * dk + i] * S[m]));
-          S[m] = sn;
-          acc = fmaf(s_r[t * dk + i], sn, acc);
+    const int t0 = c * chunk, tc = min(chunk, count - t0);
+    const float* buf = sm + (size_t)(c & 1) * chunk * R;
+    if (RPT <= 8) {
+      DrToken<RPT> ta, tb;
+      dr_read(ta, buf, dk, sub, L, vcol);
+      for (int t = 0; t < tc; t += 2) {
+        if (t + 1 < tc) dr_read(tb, buf + (size_t)(t + 1) * R, dk, sub, L, vcol);
+        const float o0 = dr_step(ta, S, L);
+        if (writer) op[(size_t)(t0 + t) * H * dv] = o0;
+        if (t + 1 < tc) {
+          if (t + 2 < tc) dr_read(ta, buf + (size_t)(t + 2) * R, dk, sub, L, vcol);
+          const float o1 = dr_step(tb, S, L);
+          if (writer) op[(size_t)(t0 + t + 1) * H * dv] = o1;
         }
       }
-      for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (col_ok && sub == 0) out[(size_t)(row0 + t0 + t) * H * dv + (size_t)h * dv + col] = acc;
+    } else {
+      for (int t = 0; t < tc; ++t) {
+        DrToken<RPT> ta;
+        dr_read(ta, buf + (size_t)t * R, dk, sub, L, vcol);
+        const float o0 = dr_step(ta, S, L);
+        if (writer) op[(size_t)(t0 + t) * H * dv] = o0;
+      }
     }
+    __syncthreads();                            // the stage may be filled again
   }
 #pragma unroll
   for (int m = 0; m < RPT; ++m) {
@@ -110,30 +196,42 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ r, const float*
   }
 }
 
+// `rec`: scratch of n * H * (5 dk + dv) floats (16-byte aligned) that the call fills and reads.
 HK_API int hk_delta_rule_scan(const float* r, const float* k, const float* v, const float* al, long long ld, const float* wl,
-                              long long ldw, const float* a_bias, const float* w_bias, const int* segs, int n_seg, float* state,
-                              float* out, int H, int dk, int dv, float decay_scale, float key_eps, void* stream) {
-  if (n_seg <= 0) return 0;
-  if (H < 1 || dk < 1 || dv < 1 || dk > DR_MAX_RPT * 32) return HK_ERR_UNSUPPORTED;
-  // lanes per column: the fewest that leave a thread at most 8 state rows while a block still has 32 threads or more
+                              long long ldw, const float* a_bias, const float* w_bias, const int* segs, int n_seg, int n_rows,
+                              float* rec, float* state, float* out, int H, int dk, int dv, float decay_scale, float key_eps,
+                              void* stream) {
+  if (n_seg <= 0 || n_rows <= 0) return 0;
+  if (H < 1 || dk < 1 || dv < 1 || dk > DR_MAX_RPT * 32 || ((uintptr_t)rec & 15)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  {
+    const long long items = (long long)n_rows * H;
+    int e = hk_launch(delta_rule_prep_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, s, r, k, v, al, ld, wl, ldw, a_bias,
+                      w_bias, rec, items, H, dk, dv, decay_scale, key_eps);
+    if (e) return e;
+  }
+  // lanes per column: the fewest that leave a thread at most 8 state rows while a block still has 64 threads or more
   int L = 1;
   while (L < 32 && (dk + L - 1) / L > 8) L <<= 1;
   while (L < 32 && dv * L < 64) L <<= 1;
   const int rpt = (dk + L - 1) / L;
+  // columns per block: few enough that one request's heads fill the SMs, many enough that a block is two warps or more
   int cols = min(dv, 256 / L);
+  while (cols > 8 && cols * L > 64 && (long long)n_seg * H * ((dv + cols - 1) / cols) < 296) cols >>= 1;
   if (cols < 1) cols = 1;
-  int threads = ((cols * L + 31) / 32) * 32;
-  const int chunk = dk > 64 ? 8 : 16;
-  const size_t smem = (size_t)chunk * (5 * dk + cols) * sizeof(float);
+  const int threads = ((cols * L + 31) / 32) * 32;
+  const int R = 5 * dk + dv;
+  int chunk = 16;
+  while (chunk > 2 && (size_t)2 * chunk * R * sizeof(float) > 96 * 1024) chunk >>= 1;
+  const size_t smem = (size_t)2 * chunk * R * sizeof(float);
   dim3 grid((unsigned)(n_seg * H), (unsigned)((dv + cols - 1) / cols));
-  cudaStream_t s = (cudaStream_t)stream;
-#define DR_LAUNCH(R)                                                                                                       \
-  do {                                                                                                                     \
-    static HkSmemCache cache;                                                                                              \
-    int e = hk_allow_smem(delta_rule_scan_kernel<R>, smem, cache);                                                         \
-    if (e) return e;                                                                                                       \
-    return hk_launch(delta_rule_scan_kernel<R>, grid, dim3(threads), smem, s, r, k, v, al, ld, wl, ldw, a_bias, w_bias,     \
-                     segs, state, out, H, dk, dv, L, cols, chunk, decay_scale, key_eps);                                   \
+#define DR_LAUNCH(RP)                                                                                                       \
+  do {                                                                                                                      \
+    static HkSmemCache cache;                                                                                               \
+    int e = hk_allow_smem(delta_rule_scan_kernel<RP>, smem, cache);                                                         \
+    if (e) return e;                                                                                                        \
+    return hk_launch(delta_rule_scan_kernel<RP>, grid, dim3(threads), smem, s, (const float*)rec, segs, state, out, H, dk, dv, \
+                     L, cols, chunk);                                                                                       \
   } while (0)
   if (rpt <= 1) DR_LAUNCH(1);
   if (rpt <= 2) DR_LAUNCH(2);
@@ -183,49 +281,79 @@ HK_API int hk_head_norm_gate(const float* o, const float* g, long long ldg, cons
 }
 
 // ------------------------------------------------------------------ minGRU
-// proj[n, 3W] = [z logits | candidate inputs | gate inputs]; a thread owns a channel of a segment.
+// proj[n, 3W] = [z logits | candidate inputs | gate inputs].  A block owns 32 channels of a segment and walks it in
+// chunks of MG_CHUNK tokens: all threads turn the chunk's inputs into a = 1 - z, b = z * c and silu(g) (in parallel,
+// the next chunk's inputs already on their way in registers), one warp runs the recurrence S <- a S + b down the
+// chunk, a channel per lane, and all threads write S * silu(g).
+#define MG_CHUNK 64
+#define MG_LANES 8      // token lanes: a thread takes every 8th token of a chunk in the parallel phases
+#define MG_PER (MG_CHUNK / MG_LANES)
+
 template <typename T>
-__global__ void mingru_scan_kernel(const float* __restrict__ proj, long long ld, const float* __restrict__ z_bias,
-                                   const float* __restrict__ x_bias, const int* __restrict__ segs, float* __restrict__ state,
-                                   T* __restrict__ out, int W) {
+__global__ void __launch_bounds__(32 * MG_LANES)
+mingru_scan_kernel(const float* __restrict__ proj, long long ld, const float* __restrict__ z_bias,
+                   const float* __restrict__ x_bias, const int* __restrict__ segs, float* __restrict__ state,
+                   T* __restrict__ out, int W) {
+  __shared__ float sa[MG_CHUNK][32], sb[MG_CHUNK][32], sg[MG_CHUNK][32];
   const int seg = blockIdx.x;
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c >= W) return;
+  const int ch = threadIdx.x & 31, tl = threadIdx.x >> 5;
+  const int c = blockIdx.y * 32 + ch;
+  const bool ok = c < W;
   const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
-  const float bz = z_bias ? z_bias[c] : 0.f, bx = x_bias ? x_bias[c] : 0.f;
-  float S = state[(size_t)slot * W + c];
-  const float* p = proj + (size_t)row0 * ld + c;
-  T* op = out + (size_t)row0 * W + c;
-  float zl = p[0], xl = p[W], gl = p[2 * (size_t)W];
-  for (int t = 0; t < count; ++t) {
-    float zn = 0.f, xn = 0.f, gn = 0.f;
-    if (t + 1 < count) {                       // the next token's inputs are asked for before this token's arithmetic
-      const float* q = p + (size_t)(t + 1) * ld;
-      zn = q[0];
-      xn = q[W];
-      gn = q[2 * (size_t)W];
+  const float bz = (ok && z_bias) ? z_bias[c] : 0.f, bx = (ok && x_bias) ? x_bias[c] : 0.f;
+  float S = (ok && tl == 0) ? state[(size_t)slot * W + c] : 0.f;
+  float zl[MG_PER], xl[MG_PER], gl[MG_PER];
+  auto fetch = [&](int t0) {
+#pragma unroll
+    for (int j = 0; j < MG_PER; ++j) {
+      const int t = t0 + tl + j * MG_LANES;
+      const bool in = ok && t < count;
+      const float* p = proj + (size_t)(row0 + (in ? t : 0)) * ld + (ok ? c : 0);
+      zl[j] = in ? p[0] : 0.f;
+      xl[j] = in ? p[W] : 0.f;
+      gl[j] = in ? p[2 * (size_t)W] : 0.f;
     }
-    const float z = sigmoid_f(zl + bz);
-    const float x = xl + bx;
-    const float cand = x >= 0.f ? x + 0.5f : sigmoid_f(x);
-    S = (1.0f - z) * S + z * cand;
-    op[(size_t)t * W] = from_f32<T>(S * (gl * sigmoid_f(gl)));
-    zl = zn;
-    xl = xn;
-    gl = gn;
+  };
+  fetch(0);
+  for (int t0 = 0; t0 < count; t0 += MG_CHUNK) {
+    const int tc = min(MG_CHUNK, count - t0);
+#pragma unroll
+    for (int j = 0; j < MG_PER; ++j) {
+      const int t = tl + j * MG_LANES;
+      const float z = sigmoid_f(zl[j] + bz);
+      const float x = xl[j] + bx;
+      const float cand = x >= 0.f ? x + 0.5f : sigmoid_f(x);
+      sa[t][ch] = 1.0f - z;
+      sb[t][ch] = z * cand;
+      sg[t][ch] = gl[j] * sigmoid_f(gl[j]);
+    }
+    __syncthreads();
+    if (t0 + MG_CHUNK < count) fetch(t0 + MG_CHUNK);      // in flight while the recurrence runs
+    if (tl == 0) {
+      for (int t = 0; t < tc; ++t) {
+        S = fmaf(sa[t][ch], S, sb[t][ch]);
+        sa[t][ch] = S;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < MG_PER; ++j) {
+      const int t = tl + j * MG_LANES;
+      if (ok && t < tc) out[(size_t)(row0 + t0 + t) * W + c] = from_f32<T>(sa[t][ch] * sg[t][ch]);
+    }
+    __syncthreads();                                     // the chunk's arrays are free again
   }
-  state[(size_t)slot * W + c] = S;
+  if (ok && tl == 0) state[(size_t)slot * W + c] = S;
 }
 
 HK_API int hk_mingru_scan(const float* proj, long long ld, const float* z_bias, const float* x_bias, const int* segs, int n_seg,
                           float* state, void* out, int out_dtype, int W, void* stream) {
   if (n_seg <= 0 || W <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  const int threads = W >= 128 ? 128 : 32 * ((W + 31) / 32);
-  dim3 grid((unsigned)n_seg, (unsigned)((W + threads - 1) / threads));
+  dim3 grid((unsigned)n_seg, (unsigned)((W + 31) / 32));
   if (out_dtype == HK_F32)
-    return hk_launch(mingru_scan_kernel<float>, grid, dim3(threads), 0, s, proj, ld, z_bias, x_bias, segs, state, (float*)out, W);
+    return hk_launch(mingru_scan_kernel<float>, grid, dim3(32 * MG_LANES), 0, s, proj, ld, z_bias, x_bias, segs, state, (float*)out, W);
   if (out_dtype == HK_BF16)
-    return hk_launch(mingru_scan_kernel<bf16>, grid, dim3(threads), 0, s, proj, ld, z_bias, x_bias, segs, state, (bf16*)out, W);
+    return hk_launch(mingru_scan_kernel<bf16>, grid, dim3(32 * MG_LANES), 0, s, proj, ld, z_bias, x_bias, segs, state, (bf16*)out, W);
   return HK_ERR_UNSUPPORTED;
 }

@@ -31,12 +31,21 @@ __global__ void route_topk_kernel(const T* __restrict__ x, const float* __restri
   if (t >= n) return;
   float* z = sm + (size_t)wid * E;
   const T* xr = x + (size_t)t * d;
-  for (int e = 0; e < E; ++e) {
-    const float* wr = w + (size_t)e * d;
-    float acc = 0.f;
-    for (int i = lane; i < d; i += 32) acc = fmaf(to_f32<T>(xr[i]), wr[i], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) z[e] = acc;
+  for (int e0 = 0; e0 < E; e0 += 8) {          // eight experts per pass over the token's vector
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      const float xv = to_f32<T>(xr[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (e0 + j < E) acc[j] = fmaf(xv, w[(size_t)(e0 + j) * d + i], acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sum = warp_sum(acc[j]);
+      if (lane == 0 && e0 + j < E) z[e0 + j] = sum;
+    }
   }
   __syncwarp();
   float first = 0.f, mine = 0.f, total = 0.f;
@@ -218,6 +227,139 @@ grouped_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, TO* __rest
   }
 }
 
+// The same on the tensor cores (bf16 operands, fp32 accumulation; K a multiple of 8): a CTA takes a tile of RT_BM
+// sorted rows and 128 weight rows: plain, 128 output columns; gated, 64 gate rows and the 64 up rows that match
+// them, so that silu(gate) * up is taken in the epilogue.  Operands come through a three-stage cp.async ring in
+// slices of 32 k (A rows gathered through `rows`), fragments by ldmatrix, products by mma.sync m16n8k16: eight
+// warps as 2 (rows) x 4 (columns), a warp 32 rows x 32 weight rows.  An output element's sum runs over k in an
+// order that does not depend on the row's place in its tile, so a token's result does not depend on the batch.
+#define GM_BN 128
+#define GM_BK 32
+#define GM_LD (GM_BK + 8)
+#define GM_STAGES 3
+
+__device__ __forceinline__ uint32_t gm_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void gm_cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(gm_smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void gm_ldmatrix_x4(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(gm_smem_u32(p)));
+}
+__device__ __forceinline__ void gm_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+grouped_gemm_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, void* __restrict__ out_, const int* __restrict__ tiles,
+                        const int* __restrict__ offsets, const int* __restrict__ perm, int top, int gather, int N, int K) {
+  __shared__ __align__(16) bf16 As[GM_STAGES][RT_BM][GM_LD];
+  __shared__ __align__(16) bf16 Ws[GM_STAGES][GM_BN][GM_LD];
+  __shared__ int rows[RT_BM];
+  const int e = tiles[2 * blockIdx.y];
+  if (e < 0) return;
+  const int p0 = tiles[2 * blockIdx.y + 1];
+  const int p_end = min(p0 + RT_BM, offsets[e + 1]);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < RT_BM) {
+    const int p = p0 + tid;
+    rows[tid] = p < p_end ? (gather ? perm[p] / top : p) : -1;
+  }
+  __syncthreads();
+  constexpr int COLS = GATED ? 64 : 128;            // output columns of a tile
+  const int n0 = blockIdx.x * COLS;
+  const bf16* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+  // what this thread copies per stage: one 16-byte piece of A, two of W
+  const int a_row = tid >> 2, a_k = (tid & 3) * 8;
+  const int a_src = rows[a_row];
+  const bf16* a_ptr = a + (size_t)max(a_src, 0) * K + a_k;
+  const bf16* w_ptr[2];
+  bool w_ok[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int r = (tid + j * 256) >> 2;              // row of the W tile
+    const int col = GATED ? (r & 63) : r;
+    const int gn = n0 + col;
+    w_ok[j] = gn < N;
+    const size_t wrow = GATED ? (size_t)(r >> 6) * N + min(gn, N - 1) : (size_t)min(gn, N - 1);
+    w_ptr[j] = we + wrow * K + a_k;
+  }
+  auto load = [&](int stage, int k0) {
+    const bool kin = k0 + a_k < K;
+    gm_cp_async16(&As[stage][a_row][a_k], a_ptr + k0, kin && a_src >= 0);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) gm_cp_async16(&Ws[stage][(tid + j * 256) >> 2][a_k], w_ptr[j] + k0, kin && w_ok[j]);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int wr = warp >> 2, wc = warp & 3;           // warp row (32 rows each), warp column
+  // the W-tile row of this warp's n8 tile nt: gated, tiles 0 and 1 are gate rows and 2 and 3 the up rows that match them
+  auto wn = [&](int nt) { return GATED ? ((nt >> 1) * 64 + wc * 16 + (nt & 1) * 8) : (wc * 32 + nt * 8); };
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+  const int ksteps = (K + GM_BK - 1) / GM_BK;
+  load(0, 0);
+  if (ksteps > 1) load(1, GM_BK); else asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int ks = 0; ks < ksteps; ++ks) {
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();                                  // stage ks has landed; stage ks - 1 is free for everyone
+    if (ks + 2 < ksteps) load((ks + 2) % GM_STAGES, (ks + 2) * GM_BK); else asm volatile("cp.async.commit_group;" ::: "memory");
+    const int st = ks % GM_STAGES;
+#pragma unroll
+    for (int kk = 0; kk < GM_BK; kk += 16) {
+      uint32_t af[2][4], bfr[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        gm_ldmatrix_x4(af[mt], &As[st][wr * 32 + mt * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int np = 0; np < 2; ++np)                 // two n8 tiles per ldmatrix: (tile, k half) = (lane / 16, (lane / 8) & 1)
+        gm_ldmatrix_x4(bfr[np], &Ws[st][wn(np * 2 + (lane >> 4)) + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) gm_mma(acc[mt][nt], af[mt], bfr[nt >> 1][(nt & 1) * 2], bfr[nt >> 1][(nt & 1) * 2 + 1]);
+    }
+  }
+  const int g = lane >> 2, t2 = (lane & 3) * 2;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int p = p0 + wr * 32 + mt * 16 + g + half * 8;
+      if (p >= p_end) continue;
+      if (GATED) {
+        bf16* out = reinterpret_cast<bf16*>(out_);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int gn = n0 + wc * 16 + nt * 8 + t2 + c;
+            if (gn >= N) continue;
+            const float gate = acc[mt][nt][half * 2 + c], up = acc[mt][nt + 2][half * 2 + c];
+            out[(size_t)p * N + gn] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+          }
+      } else {
+        float* out = reinterpret_cast<float*>(out_);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int gn = n0 + wc * 32 + nt * 8 + t2 + c;
+            if (gn < N) out[(size_t)p * N + gn] = acc[mt][nt][half * 2 + c];
+          }
+      }
+    }
+}
+
 HK_API int hk_grouped_gemm(const void* a, const void* w, int dtype, void* out, const int* tiles, int max_tiles, const int* offsets,
                            const int* perm, int top, int gather, int N, int K, int gated, void* stream) {
   if (max_tiles <= 0 || N <= 0) return 0;
@@ -230,6 +372,16 @@ HK_API int hk_grouped_gemm(const void* a, const void* w, int dtype, void* out, c
                        tiles, offsets, perm, top, gather, N, K);
     return hk_launch(grouped_gemm_kernel<float, float, false>, grid, dim3(256), 0, s, (const float*)a, (const float*)w, (float*)out,
                      tiles, offsets, perm, top, gather, N, K);
+  }
+  if (dtype == HK_BF16 && (K & 7) == 0 && ((((uintptr_t)a | (uintptr_t)w) & 15) == 0)) {
+    if (gated) {
+      dim3 g2((unsigned)((N + 63) / 64), (unsigned)max_tiles);
+      return hk_launch(grouped_gemm_mma_kernel<true>, g2, dim3(256), 0, s, (const bf16*)a, (const bf16*)w, out, tiles, offsets, perm,
+                       top, gather, N, K);
+    }
+    dim3 g2((unsigned)((N + GM_BN - 1) / GM_BN), (unsigned)max_tiles);
+    return hk_launch(grouped_gemm_mma_kernel<false>, g2, dim3(256), 0, s, (const bf16*)a, (const bf16*)w, out, tiles, offsets, perm,
+                     top, gather, N, K);
   }
   if (dtype == HK_BF16) {
     if (gated)

@@ -1,0 +1,269 @@
+"""Throughput of a model design beside the closest existing one at equal size (`bench.py --design NAME`).
+
+For each size: a prompt of 2,048 tokens in one step (tokens/s) and decode steps at batch 8 and 64 over 2,048-token
+contexts (tokens/s), through `Engine.step` with random weights in bfloat16, timed on the device with CUDA events
+(warm-up first; a prefill reads or writes far more than L2 holds, a decode step streams every weight).  Then the
+design's own kernels one by one at that size, each with the bytes it must move and the floating-point operations
+it must do, so that its distance from the roofline (the larger of bytes / measured copy bandwidth and operations /
+peak) can be read beside the like kernel of the other model.  L2 is flushed between the timed launches of a kernel.
+"""
+from __future__ import annotations
+
+import json
+import math
+import sys
+import time
+
+FP32_TFLOPS = 2 * 148 * 128 * 1.9e-3        # fp32 FMA peak of 148 SMs x 128 lanes at 1.9 GHz (nominal): the scans' ceiling
+
+
+def kedanex_shape(width: int, groups: int = 2, vocab: int = 32000, window: int = 1024) -> dict:
+    """Layer sizes that resemble a real model's: delta rule with heads of 64, attention with heads of 128 and four
+    query heads per key head, a minGRU as wide as the model, a dense feed-forward of three times the width and eight
+    experts of half the width of which two are used; one layer of every group runs with the first layer's tensors."""
+    heads64, heads128 = width // 64, width // 128
+    delta = {"type": "general_delta", "mixer": {"dim": 64, "heads": heads64, "decay_rank": 64}}
+    att = {"type": "attention", "mixer": {"dim": 128, "heads": heads128, "kv_heads": max(1, heads128 // 4), "vdim": 128,
+                                          "mask": {"size": window}, "rot": {"base": 1000000.0, "dims": 128},
+                                          "scale": 1.0 / math.sqrt(128.0)}}
+    gru = {"type": "mingru", "mixer": {"width": width}}
+    dense = {"kind": "dense", "ff": 3 * width}
+    moe = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 8, "top": 2}}
+    layers = []
+    for g in range(groups):
+        first = len(layers)
+        layers += [dict(delta, mlp=dense), dict(att, mlp=moe), dict(gru, mlp=moe), dict(delta, mlp=dense, weights_of=first)]
+    return {"architecture": "Kedanex", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "layers": layers,
+            "initializer_range": 0.02}
+
+
+def qwen3_shape(width: int, layers: int, vocab: int = 32000) -> dict:
+    return dict(architectures=["Qwen3ForCausalLM"], hidden_size=width, num_hidden_layers=layers, intermediate_size=3 * width,
+                num_attention_heads=width // 128, num_key_value_heads=max(1, width // 512), head_dim=128, vocab_size=vocab,
+                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=8192,
+                initializer_range=0.02)
+
+
+def _events():
+    import torch
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def model_points(raw: dict, prompt: int, batches, steps: int, warmup: int, reps: int) -> dict:
+    import numpy as np
+    import torch
+
+    from .config import config_from_dict
+    from .csrc import ops
+    from .engine import Engine, StepEntry
+    cfg = config_from_dict(raw)
+    rng = np.random.default_rng(3)
+    vocab = cfg.vocab_size
+    out = {}
+    per_req = -(-(prompt + warmup + steps + 8) // 64) * 64
+    for batch in batches:
+        eng = Engine(config=cfg, random_seed=5, dtype="bfloat16", max_tokens=batch * per_req, page_tokens=64, max_requests=batch,
+                     max_context=per_req, max_batch_tokens=max(prompt, batch))
+        if "params" not in out:
+            out["params"] = int(sum(int(np.prod(s.shape)) for s in eng.model.param_specs().values()))
+        if "prefill" not in out:
+            ids = rng.integers(0, vocab, prompt).tolist()
+            times = []
+            for i in range(reps + 2):
+                eng.open_request("p")
+                a, b = _events()
+                torch.cuda.synchronize()
+                a.record()
+                eng.step([StepEntry("p", ids, [prompt - 1])])
+                b.record()
+                torch.cuda.synchronize()
+                eng.close_request("p")
+                if i > 1:
+                    times.append(a.elapsed_time(b))
+            ms = float(np.median(times))
+            out["prefill"] = {"tokens": prompt, "ms": ms, "tok_s": prompt / ms * 1e3}
+        names = [f"d{i}" for i in range(batch)]
+        for r in names:
+            eng.open_request(r)
+        group = max(1, eng.max_batch_tokens // prompt)
+        for i in range(0, batch, group):
+            eng.step([StepEntry(r, rng.integers(0, vocab, prompt).tolist(), []) for r in names[i:i + group]])
+        toks = rng.integers(0, vocab, (warmup + steps, batch))
+        pick = torch.empty(batch, dtype=torch.int32, device=eng.device)
+
+        def one(s):
+            ops.argmax(eng.step([StepEntry(r, [int(toks[s, i])], [0]) for i, r in enumerate(names)]), pick)
+
+        for s in range(warmup):
+            one(s)
+        a, b = _events()
+        torch.cuda.synchronize()
+        l0 = ops.launch_count()
+        a.record()
+        for s in range(warmup, warmup + steps):
+            one(s)
+        b.record()
+        torch.cuda.synchronize()
+        eng.check_kernel_status()
+        ms = a.elapsed_time(b) / steps
+        out[f"decode_b{batch}"] = {"ms": ms, "tok_s": batch / ms * 1e3, "launches_per_step": (ops.launch_count() - l0) / steps}
+        for r in names:
+            eng.close_request(r)
+        del eng
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
+def _time_kernel(fn, reps: int = 7):
+    """Median device time in microseconds of `fn()`, L2 flushed before every timed call."""
+    import torch
+    flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
+    times = []
+    for i in range(reps + 3):
+        flush.fill_(float(i))
+        a, b = _events()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(a.elapsed_time(b) * 1e3)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def kernel_points(width: int, n: int, peaks: dict) -> dict:
+    """The design's kernels alone at `n` rows of a layer of this width, and the like kernels of the Qwen3 decoder."""
+    import numpy as np
+    import torch
+
+    from .csrc import ops
+    dev = "cuda"
+    bw, tc = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    out = {}
+
+    def note(name, us, nbytes, flops, peak_flops, like=None):
+        floor = max(nbytes / bw, flops / peak_flops if peak_flops else 0.0) * 1e6
+        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "flops": int(flops), "roofline_us": round(floor, 2),
+                     "of_roofline": round(floor / us, 3), **({"like": like} if like else {})}
+
+    def segs(count, rows):
+        return torch.tensor([[i, i * rows, rows] for i in range(count)], dtype=torch.int32, device=dev)
+
+    # ---- delta rule scan: one request of n rows; and n requests of one row (a decode step)
+    H, dk = width // 64, 64
+    K = H * dk
+    proj = torch.randn(n, 4 * K, device=dev) * 0.5
+    wl = torch.randn(n, K, device=dev)
+    ab, wb = torch.zeros(K, device=dev), torch.zeros(K, device=dev)
+    o = torch.empty(n, K, device=dev)
+    for label, count, rows in (("delta_rule_scan (1 request)", 1, n), ("delta_rule_scan (8 requests)", 8, n // 8),
+                               ("delta_rule_scan (decode, 64 requests)", 64, 1)):
+        state = torch.zeros(count, H, dk, dk, device=dev)
+        m = count * rows
+        sg = segs(count, rows)
+        us = _time_kernel(lambda: ops.delta_rule_scan(proj[:m, :K], proj[:m, K:2 * K], proj[:m, 2 * K:3 * K], proj[:m, 3 * K:], wl[:m], ab,
+                                                      wb, sg, state, o[:m], H, dk, dk, math.exp(-0.5), 1e-6))
+        note(label, us, 4 * (6 * m * K + 2 * count * H * dk * dk), 8.0 * m * H * dk * dk, FP32_TFLOPS * 1e12,
+             like="paged attention (same rows)")
+    g = torch.randn(n, K, device=dev)
+    og = torch.empty(n, K, dtype=torch.bfloat16, device=dev)
+    us = _time_kernel(lambda: ops.head_norm_gate(o, g, torch.ones(K, device=dev), 1e-5, og, H, dk))
+    note("head_norm_gate", us, n * K * (4 + 4 + 2), 0, 0, like="rms_norm")
+    # ---- minGRU scan
+    proj3 = torch.randn(n, 3 * width, device=dev)
+    outb = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
+    zb = torch.zeros(width, device=dev)
+    for label, count, rows in (("mingru_scan (1 request)", 1, n), ("mingru_scan (8 requests)", 8, n // 8), ("mingru_scan (decode, 64 requests)", 64, 1)):
+        state = torch.zeros(count, width, device=dev)
+        m = count * rows
+        sg = segs(count, rows)
+        us = _time_kernel(lambda: ops.mingru_scan(proj3[:m], zb, zb, sg, state, outb[:m]))
+        note(label, us, m * width * (12 + 2), 0, 0, like="swiglu / rms_norm (row-wise)")
+    # ---- norms and the polynomial activation
+    x = torch.randn(n, width, device=dev)
+    res = torch.randn(n, width, device=dev)
+    wn = torch.ones(width, device=dev)
+    us = _time_kernel(lambda: ops.rms_norm_add(x, wn, 1e-5, res))
+    note("rms_norm_add", us, n * width * 12, 0, 0, like="rms_norm")
+    xb = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
+    us = _time_kernel(lambda: ops.rms_norm(x, wn, 1e-5, xb))
+    note("rms_norm (Qwen3 and this design)", us, n * width * 6, 0, 0)
+    F = 3 * width
+    z = torch.randn(n, F, device=dev)
+    hb = torch.empty(n, F, dtype=torch.bfloat16, device=dev)
+    coef = torch.ones(4, device=dev)
+    us = _time_kernel(lambda: ops.polynorm(z, coef, 1e-5, hb))
+    note("polynorm", us, n * F * 6, 0, 0, like="swiglu")
+    gu = torch.randn(n, 2 * F, device=dev)
+    us = _time_kernel(lambda: ops.swiglu(gu, hb))
+    note("swiglu (Qwen3, unfused form)", us, n * F * 10, 0, 0)
+    # ---- routed feed-forward: route, sort, the two grouped products, combine
+    E, top, Fe = 8, 2, width // 2
+    xb.copy_(torch.randn(n, width, device=dev))
+    wr = torch.randn(E, width, device=dev) * 0.1
+    ids = torch.empty(n, top, dtype=torch.int32, device=dev)
+    wts = torch.empty(n, top, device=dev)
+    us = _time_kernel(lambda: ops.route_topk(xb, wr, ids, wts))
+    note("route_topk", us, n * width * 2 + E * width * 4, 2.0 * n * E * width, FP32_TFLOPS * 1e12)
+    pairs = n * top
+    tile_rows = ops.route_tile_rows()
+    max_tiles = pairs // tile_rows + min(E, pairs)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    perm = torch.empty(pairs, dtype=torch.int32, device=dev)
+    inv = torch.empty(pairs, dtype=torch.int32, device=dev)
+    tiles = torch.empty(max_tiles, 2, dtype=torch.int32, device=dev)
+    us = _time_kernel(lambda: ops.route_sort(ids, E, offsets, perm, inv, tiles))
+    note("route_sort", us, pairs * 16, 0, 0)
+    wgu = (torch.randn(E, 2 * Fe, width, device=dev) * 0.02).bfloat16()
+    wd = (torch.randn(E, width, Fe, device=dev) * 0.02).bfloat16()
+    h = torch.empty(pairs, Fe, dtype=torch.bfloat16, device=dev)
+    ys = torch.empty(pairs, width, device=dev)
+    used = min(E, pairs)
+    us = _time_kernel(lambda: ops.grouped_gemm(xb, wgu, h, tiles, offsets, perm, top, gather=True, gated=True))
+    note("grouped gate/up product + SwiGLU", us, used * 2 * Fe * width * 2 + n * width * 2 + pairs * Fe * 2, 2.0 * pairs * 2 * Fe * width, tc,
+         like="gate/up product with SwiGLU epilogue (same FLOPs)")
+    us = _time_kernel(lambda: ops.grouped_gemm(h, wd, ys, tiles, offsets, perm, top, gather=False, gated=False))
+    note("grouped down product", us, used * Fe * width * 2 + pairs * (Fe * 2 + width * 4), 2.0 * pairs * Fe * width, tc,
+         like="down product (same FLOPs)")
+    y = torch.empty(n, width, device=dev)
+    us = _time_kernel(lambda: ops.route_combine(ys, inv, wts, y))
+    note("route_combine", us, pairs * width * 4 + n * width * 4, 0, 0)
+    # the like products of the dense decoder: the same FLOPs as the routed pair (pairs rows, Fe wide)
+    wq = (torch.randn(2 * Fe, width, device=dev) * 0.02).bfloat16()
+    a2 = torch.randn(pairs, width, device=dev).bfloat16()
+    us = _time_kernel(lambda: ops.gemm_swiglu(a2, wq, h))
+    note("dense gate/up product + SwiGLU (Qwen3; rows = pairs)", us, 2 * Fe * width * 2 + pairs * (width + Fe) * 2, 2.0 * pairs * 2 * Fe * width, tc)
+    wd2 = wd[0].contiguous()
+    us = _time_kernel(lambda: ops.gemm(h, wd2, ys))
+    note("dense down product (Qwen3; rows = pairs)", us, Fe * width * 2 + pairs * (Fe * 2 + width * 4), 2.0 * pairs * Fe * width, tc)
+    return out
+
+
+def run(design: str, args, peaks: dict) -> dict:
+    if design != "kedanex":
+        raise SystemExit(f"bench.py --design: unknown design '{design}' (known: kedanex)")
+    widths = [int(w) for w in str(args.design_widths).split(",")]
+    sizes = {}
+    for width in widths:
+        t0 = time.time()
+        ours = kedanex_shape(width)
+        theirs = qwen3_shape(width, len(ours["layers"]))
+        entry = {"kedanex": model_points(ours, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
+                 "qwen3": model_points(theirs, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
+                 "layer_runs": len(ours["layers"])}
+        entry["kernels_prefill_2048_rows"] = kernel_points(width, 2048, peaks)
+        entry["kernels_decode_64_rows"] = {k: v for k, v in kernel_points(width, 64, peaks).items() if "request" not in k or "decode" in k}
+        sizes[f"width{width}"] = entry
+        print(f"[bench] design {design}, width {width}: {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+    k = sizes[f"width{widths[-1]}"]
+    return {"metric": f"{design} prefill and decode tok/s beside Qwen3 at equal width and depth", "value": k["kedanex"]["decode_b8"]["tok_s"],
+            "unit": "tokens/s (decode, batch 8, largest width)", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "higher_is_better": True, "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random-init weights",
+            "impl": "ours", "design": design, "sizes": sizes, "peaks": peaks}
+
+
+if __name__ == "__main__":
+    print(json.dumps(kedanex_shape(2048), indent=1))

@@ -80,7 +80,7 @@ class GQAAttention(Part):
         if not bfloat16 or self.vd != self.hd or not attention_fast.supported(self.hd, self.H // self.G):
             return ()
         return ("attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.hd, self.H // self.G) \
-            else ("attention_flash",)
+            and not self.sink else ("attention_flash",)
 
     def children(self):
         return (self.position,) if self.position is not None else ()
@@ -125,7 +125,7 @@ class GQAAttention(Part):
             self.k_norm = tensors[p + nm["k_norm"]]
         from ..csrc import attention_fast
         if precision.compute == torch.bfloat16 and attention_fast.supported(self.hd, self.H // self.G) and self.vd == self.hd:
-            self._tables_key = ("paged_attention_items", self.window or 0, self.H, self.G, self.hd)
+            self._tables_key = ("paged_attention_items", self.window or 0, self.H, self.G, self.hd, self.sink)
             self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
 
     # -- the step's work items (host-built; see parts.base) --------------------------------
@@ -137,7 +137,8 @@ class GQAAttention(Part):
         not change (a captured decode graph) every request's keys go to the same number of splits."""
         from ..csrc import attention_fast
         H, G, hd = self.H, self.G, self.hd
-        tc = attention_fast.tc_prefill_supported(hd, H // G) and ops.forced("attention") != "flash_cp"
+        # the tcgen05 prompt kernels have no sink term: a mixer with a sink takes the mma.sync flash kernel for prompts
+        tc = attention_fast.tc_prefill_supported(hd, H // G) and ops.forced("attention") != "flash_cp" and not self.sink
         rows = 128 if tc else 64
         # the kernel with two query tiles per CTA is the faster one per row, but halves the number of work items: it
         # is taken when its items still fill the SMs (measured on the 8B layer: equal at 1,024 prompt tokens = 128
