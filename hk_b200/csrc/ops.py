@@ -463,7 +463,7 @@ def delta_rule_scan(r, k, v, a_logit, w_logit, a_bias, w_bias, segments, state, 
     lib = build.load("recurrent")
     # what every token brings to the scan (decay, removal times unit key, unit key, key, receptance, value), made by a
     # kernel of its own for all tokens at once
-    rec = torch.empty(n * H * (5 * dk + dv), dtype=torch.float32, device=out.device)
+    rec = torch.empty(n * H * int(lib.hk_delta_rule_record(dk, dv)), dtype=torch.float32, device=out.device)
     _check(lib.hk_delta_rule_scan(_ptr(r), _ptr(k), _ptr(v), _ptr(a_logit), ctypes.c_longlong(ld), _ptr(w_logit),
                                   ctypes.c_longlong(ldw), _ptr(a_bias), _ptr(w_bias), _ptr(segments), int(segments.shape[0]), n,
                                   _ptr(rec), _ptr(state), _ptr(out), H, dk, dv, ctypes.c_float(decay_scale),

@@ -24,12 +24,14 @@
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // ------------------------------------------------------------------ generalised delta rule: what a token brings
-// One warp per (token, head) writes the record [d | a*u | u | k | r | v] (5 dk + dv floats) that the scan reads:
-// everything that does not depend on the state is computed here, for all tokens at once.
+// One warp per (token, head) writes the record that the scan reads: five vectors of P = L * RPT floats (d, a*u, u, k, r;
+// P >= dk, the rest zero) and the dv values.  Inside a vector, entry i sits at (i % L) * RPT + i / L: lane `sub` of a
+// column's L lanes owns the entries i = sub, sub + L, ... and finds them side by side.  Everything that does not depend
+// on the state is computed here, for all tokens at once.
 __global__ void delta_rule_prep_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
                                        const float* __restrict__ al, long long ld, const float* __restrict__ wl, long long ldw,
                                        const float* __restrict__ a_bias, const float* __restrict__ w_bias, float* __restrict__ rec,
-                                       long long items, int H, int dk, int dv, float decay_scale, float key_eps) {
+                                       long long items, int H, int dk, int dv, int L, int RPT, float decay_scale, float key_eps) {
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (item >= items) return;
@@ -44,89 +46,51 @@ __global__ void delta_rule_prep_kernel(const float* __restrict__ r, const float*
   }
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss + key_eps);
-  float* out = rec + (size_t)item * (5 * dk + dv);
-  for (int i = lane; i < dk; i += 32) {
-    const float kv = kp[i];
-    const float u = kv * inv;
-    const float a = sigmoid_f(al[row * ld + hoff + i] + a_bias[hoff + i]);
-    out[i] = expf(-decay_scale * sigmoid_f(wl[row * ldw + hoff + i] + w_bias[hoff + i]));
-    out[dk + i] = a * u;
-    out[2 * dk + i] = u;
-    out[3 * dk + i] = kv;
-    out[4 * dk + i] = r[row * ld + hoff + i];
+  const int P = L * RPT;
+  float* out = rec + (size_t)item * (5 * P + dv);
+  for (int j = lane; j < P; j += 32) {
+    const int i = (j % RPT) * L + j / RPT;       // the entry that sits at place j
+    float d = 0.f, au = 0.f, u = 0.f, kv = 0.f, rv = 0.f;
+    if (i < dk) {
+      kv = kp[i];
+      u = kv * inv;
+      au = sigmoid_f(al[row * ld + hoff + i] + a_bias[hoff + i]) * u;
+      d = expf(-decay_scale * sigmoid_f(wl[row * ldw + hoff + i] + w_bias[hoff + i]));
+      rv = r[row * ld + hoff + i];
+    }
+    out[j] = d;
+    out[P + j] = au;
+    out[2 * P + j] = u;
+    out[3 * P + j] = kv;
+    out[4 * P + j] = rv;
   }
-  for (int c = lane; c < dv; c += 32) out[5 * dk + c] = v[row * ld + (size_t)h * dv + c];
+  for (int c = lane; c < dv; c += 32) out[5 * P + c] = v[row * ld + (size_t)h * dv + c];
 }
 
 // ------------------------------------------------------------------ generalised delta rule: the scan
-// A block owns `cols` columns of one head's state for one segment.  Records arrive in chunks of `chunk` tokens through
-// a two-stage cp.async ring (the next chunk is on its way while this one is walked).  Per token the chain that the next
-// token waits for is: u . S (registers, two partial sums, L lanes by shuffle), then one fused update per state entry;
-// the output's dot product hangs off that chain.  With at most 8 state rows per thread the next token's vectors are
-// read into registers while this token's arithmetic runs.
-#define DR_MAX_RPT 32   // state rows a thread holds at most: dk <= 32 * L, L <= 32
-
+// A block owns `cols` columns of one head's state for one segment; a column's state entries are spread over L lanes, RPT
+// per lane, in registers.  Records arrive in chunks of `chunk` tokens through a two-stage cp.async ring (the next chunk is
+// on its way while this one is walked) and are read with 16-byte loads.  Per token the chain that the next token waits
+// for is: u . S (four partial sums, then L lanes by shuffle), then one fused update per state entry; the output's dot
+// product hangs off that chain.  How many lanes share a column is chosen by the launcher: one lane (no shuffle, the fewest
+// instructions) when requests and heads alone give the SMs enough warps, more when a single request must be spread out.
 __device__ __forceinline__ void dr_cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <int RPT>
-struct DrToken {
-  float d[RPT], au[RPT], u[RPT], k[RPT], r[RPT], v;
-};
-
-template <int RPT>
-__device__ __forceinline__ void dr_read(DrToken<RPT>& t, const float* rec, int dk, int sub, int L, int vcol) {
-#pragma unroll
-  for (int m = 0; m < RPT; ++m) {
-    const int i = sub + L * m;
-    const bool ok = i < dk;
-    t.d[m] = ok ? rec[i] : 0.f;
-    t.au[m] = ok ? rec[dk + i] : 0.f;
-    t.u[m] = ok ? rec[2 * dk + i] : 0.f;
-    t.k[m] = ok ? rec[3 * dk + i] : 0.f;
-    t.r[m] = ok ? rec[4 * dk + i] : 0.f;
-  }
-  t.v = rec[5 * dk + vcol];
-}
-
-template <int RPT>
-__device__ __forceinline__ float dr_step(const DrToken<RPT>& t, float (&S)[RPT], int L) {
-  float du0 = 0.f, du1 = 0.f;
-#pragma unroll
-  for (int m = 0; m < RPT; m += 2) {
-    du0 = fmaf(t.u[m], S[m], du0);
-    if (m + 1 < RPT) du1 = fmaf(t.u[m + 1], S[m + 1], du1);
-  }
-  float du = du0 + du1;
-  for (int o = L >> 1; o > 0; o >>= 1) du += __shfl_xor_sync(0xffffffffu, du, o);
-  float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-  for (int m = 0; m < RPT; m += 2) {
-    S[m] = fmaf(t.k[m], t.v, fmaf(-t.au[m], du, t.d[m] * S[m]));
-    a0 = fmaf(t.r[m], S[m], a0);
-    if (m + 1 < RPT) {
-      S[m + 1] = fmaf(t.k[m + 1], t.v, fmaf(-t.au[m + 1], du, t.d[m + 1] * S[m + 1]));
-      a1 = fmaf(t.r[m + 1], S[m + 1], a1);
-    }
-  }
-  float acc = a0 + a1;
-  for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  return acc;
-}
-
-template <int RPT>
-__global__ void delta_rule_scan_kernel(const float* __restrict__ rec, const int* __restrict__ segs, float* __restrict__ state,
-                                       float* __restrict__ out, int H, int dk, int dv, int L, int cols, int chunk) {
-  extern __shared__ __align__(16) float sm[];   // [2][chunk][5 dk + dv]
-  const int R = 5 * dk + dv;
+template <int RPT, int L>
+__global__ void __launch_bounds__(256)
+delta_rule_scan_kernel(const float* __restrict__ rec, const int* __restrict__ segs, float* __restrict__ state,
+                       float* __restrict__ out, int H, int dk, int dv, int cols, int chunk) {
+  extern __shared__ __align__(16) float sm[];   // [2][chunk][5 P + dv]
+  constexpr int P = L * RPT;
+  const int R = 5 * P + dv;
   const int seg = blockIdx.x / H, h = blockIdx.x % H;
   const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
   const int col0 = blockIdx.y * cols;
   const int tid = threadIdx.x;
   const int sub = tid % L, cidx = tid / L, col = col0 + cidx;
   const bool col_ok = cidx < cols && col < dv;
-  const int vcol = min(col, dv - 1);
   float S[RPT];
   float* sp = state + ((size_t)slot * H + h) * dk * dv;
 #pragma unroll
@@ -134,27 +98,20 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ rec, const int*
     const int i = sub + L * m;
     S[m] = (col_ok && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
   }
-  const bool vec = (R & 3) == 0;                // records are whole 16-byte pieces (the base is 16-byte aligned)
+  const int pieces = R >> 2;                    // records are whole 16-byte pieces: P is a multiple of 8, dv of 4
   auto fetch = [&](int c) {                     // chunk c -> stage c & 1
     const int t0 = c * chunk, tc = min(chunk, count - t0);
     float* dst = sm + (size_t)(c & 1) * chunk * R;
-    if (vec) {
-      const int pieces = R >> 2;
-      for (int i = tid; i < tc * pieces; i += blockDim.x) {
-        const int t = i / pieces, p = i % pieces;
-        dr_cp_async16(dst + (size_t)t * R + 4 * p, rec + ((size_t)(row0 + t0 + t) * H + h) * R + 4 * p);
-      }
-    } else {
-      for (int i = tid; i < tc * R; i += blockDim.x) {
-        const int t = i / R, p = i % R;
-        dst[(size_t)t * R + p] = rec[((size_t)(row0 + t0 + t) * H + h) * R + p];
-      }
-    }
+    const float* src = rec + ((size_t)(row0 + t0) * H + h) * R;
+    for (int t = 0; t < tc; ++t)
+      for (int p = tid; p < pieces; p += blockDim.x) dr_cp_async16(dst + (size_t)t * R + 4 * p, src + (size_t)t * H * R + 4 * p);
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   const int nchunks = (count + chunk - 1) / chunk;
   float* op = out + (size_t)row0 * H * dv + (size_t)h * dv + col;
+  const size_t ostep = (size_t)H * dv;
   const bool writer = col_ok && sub == 0;
+  const int mine = sub * RPT, vat = 5 * P + min(col, dv - 1);
   fetch(0);
   for (int c = 0; c < nchunks; ++c) {
     if (c + 1 < nchunks) {
@@ -164,29 +121,47 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ rec, const int*
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    const int t0 = c * chunk, tc = min(chunk, count - t0);
-    const float* buf = sm + (size_t)(c & 1) * chunk * R;
-    if (RPT <= 8) {
-      DrToken<RPT> ta, tb;
-      dr_read(ta, buf, dk, sub, L, vcol);
-      for (int t = 0; t < tc; t += 2) {
-        if (t + 1 < tc) dr_read(tb, buf + (size_t)(t + 1) * R, dk, sub, L, vcol);
-        const float o0 = dr_step(ta, S, L);
-        if (writer) op[(size_t)(t0 + t) * H * dv] = o0;
-        if (t + 1 < tc) {
-          if (t + 2 < tc) dr_read(ta, buf + (size_t)(t + 2) * R, dk, sub, L, vcol);
-          const float o1 = dr_step(tb, S, L);
-          if (writer) op[(size_t)(t0 + t + 1) * H * dv] = o1;
-        }
+    const int tc = min(chunk, count - c * chunk);
+    const float* buf = sm + (size_t)(c & 1) * chunk * R + mine;
+    const float* vbuf = sm + (size_t)(c & 1) * chunk * R + vat;
+#pragma unroll 2
+    for (int t = 0; t < tc; ++t) {
+      const float* tok = buf + (size_t)t * R;
+      float du0 = 0.f, du1 = 0.f, du2 = 0.f, du3 = 0.f;
+#pragma unroll
+      for (int q = 0; q < RPT / 4; ++q) {
+        const float4 u = *reinterpret_cast<const float4*>(tok + 2 * P + 4 * q);
+        du0 = fmaf(u.x, S[4 * q], du0);
+        du1 = fmaf(u.y, S[4 * q + 1], du1);
+        du2 = fmaf(u.z, S[4 * q + 2], du2);
+        du3 = fmaf(u.w, S[4 * q + 3], du3);
       }
-    } else {
-      for (int t = 0; t < tc; ++t) {
-        DrToken<RPT> ta;
-        dr_read(ta, buf + (size_t)t * R, dk, sub, L, vcol);
-        const float o0 = dr_step(ta, S, L);
-        if (writer) op[(size_t)(t0 + t) * H * dv] = o0;
+      float du = (du0 + du1) + (du2 + du3);
+#pragma unroll
+      for (int o = L >> 1; o > 0; o >>= 1) du += __shfl_xor_sync(0xffffffffu, du, o);
+      const float v = vbuf[(size_t)t * R];
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int q = 0; q < RPT / 4; ++q) {
+        const float4 d = *reinterpret_cast<const float4*>(tok + 4 * q);
+        const float4 au = *reinterpret_cast<const float4*>(tok + P + 4 * q);
+        const float4 k = *reinterpret_cast<const float4*>(tok + 3 * P + 4 * q);
+        const float4 r = *reinterpret_cast<const float4*>(tok + 4 * P + 4 * q);
+        S[4 * q] = fmaf(k.x, v, fmaf(-au.x, du, d.x * S[4 * q]));
+        S[4 * q + 1] = fmaf(k.y, v, fmaf(-au.y, du, d.y * S[4 * q + 1]));
+        S[4 * q + 2] = fmaf(k.z, v, fmaf(-au.z, du, d.z * S[4 * q + 2]));
+        S[4 * q + 3] = fmaf(k.w, v, fmaf(-au.w, du, d.w * S[4 * q + 3]));
+        a0 = fmaf(r.x, S[4 * q], a0);
+        a1 = fmaf(r.y, S[4 * q + 1], a1);
+        a2 = fmaf(r.z, S[4 * q + 2], a2);
+        a3 = fmaf(r.w, S[4 * q + 3], a3);
       }
+      float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+      for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (writer) op[(size_t)t * ostep] = acc;
     }
+    op += (size_t)tc * ostep;
     __syncthreads();                            // the stage may be filled again
   }
 #pragma unroll
@@ -196,50 +171,140 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ rec, const int*
   }
 }
 
-// `rec`: scratch of n * H * (5 dk + dv) floats (16-byte aligned) that the call fills and reads.
+// The plain form of the scan for value sizes that are no multiple of 4 (records that are not whole 16-byte pieces):
+// the same recurrence, the state in shared memory, records read with plain loads, one token at a time.
+__global__ void delta_rule_scan_plain_kernel(const float* __restrict__ rec, const int* __restrict__ segs, float* __restrict__ state,
+                                             float* __restrict__ out, int H, int dk, int dv, int L, int RPT, int cols) {
+  extern __shared__ __align__(16) float sm[];   // [blockDim / L][P] the state columns; then one record
+  const int P = L * RPT, R = 5 * P + dv;
+  const int seg = blockIdx.x / H, h = blockIdx.x % H;
+  const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
+  const int tid = threadIdx.x, sub = tid % L, cidx = tid / L, col = blockIdx.y * cols + cidx;
+  const bool col_ok = cidx < cols && col < dv;
+  float* Sc = sm + (size_t)cidx * P;             // this column's state, in the record's order of entries
+  float* recs = sm + (size_t)(blockDim.x / L) * P;
+  float* sp = state + ((size_t)slot * H + h) * dk * dv;
+  for (int m = 0; m < RPT; ++m) {
+    const int i = sub + L * m;
+    Sc[sub * RPT + m] = (col_ok && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
+  }
+  for (int t = 0; t < count; ++t) {
+    __syncthreads();
+    const float* src = rec + ((size_t)(row0 + t) * H + h) * R;
+    for (int p = tid; p < R; p += blockDim.x) recs[p] = src[p];
+    __syncthreads();
+    const float* mine = recs + sub * RPT;
+    float du0 = 0.f, du1 = 0.f;
+    for (int m = 0; m < RPT; m += 2) {
+      du0 = fmaf(mine[2 * P + m], Sc[sub * RPT + m], du0);
+      if (m + 1 < RPT) du1 = fmaf(mine[2 * P + m + 1], Sc[sub * RPT + m + 1], du1);
+    }
+    float du = du0 + du1;
+    for (int o = L >> 1; o > 0; o >>= 1) du += __shfl_xor_sync(0xffffffffu, du, o);
+    const float vj = recs[5 * P + min(col, dv - 1)];
+    float a0 = 0.f, a1 = 0.f;
+    for (int m = 0; m < RPT; ++m) {
+      const float sn = fmaf(mine[3 * P + m], vj, fmaf(-mine[P + m], du, mine[m] * Sc[sub * RPT + m]));
+      Sc[sub * RPT + m] = sn;
+      if (m & 1) a1 = fmaf(mine[4 * P + m], sn, a1); else a0 = fmaf(mine[4 * P + m], sn, a0);
+    }
+    float acc = a0 + a1;
+    for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (col_ok && sub == 0) out[(size_t)(row0 + t) * H * dv + (size_t)h * dv + col] = acc;
+  }
+  for (int m = 0; m < RPT; ++m) {
+    const int i = sub + L * m;
+    if (col_ok && i < dk) sp[(size_t)i * dv + col] = Sc[sub * RPT + m];
+  }
+}
+
+// How a column's dk state entries are laid over lanes: L lanes with RPT entries each (RPT in 8, 16, 32, 64; L * RPT >= dk
+// with as little padding as there can be).  `spread` asks for at least that many lanes: more warps for a small batch.
+static void dr_layout(int dk, int spread, int* L_out, int* rpt_out) {
+  int L = 1;
+  while (L < 32 && (dk + L - 1) / L > 64) L <<= 1;
+  while (L < 32 && L < spread && (dk + 2 * L - 1) / (2 * L) >= 8) L <<= 1;
+  int rpt = 8;
+  while (rpt < 64 && rpt * L < dk) rpt <<= 1;
+  *L_out = L;
+  *rpt_out = rpt * L >= dk ? rpt : 0;           // 0: dk above 2,048
+}
+
+// The most scratch floats per (token, head) that `hk_delta_rule_scan` may need in `rec`, whatever layout it chooses.
+HK_API int hk_delta_rule_record(int dk, int dv) {
+  int most = 0;
+  for (int spread = 1; spread <= 32; spread <<= 1) {
+    int L, rpt;
+    dr_layout(dk, spread, &L, &rpt);
+    if (rpt && 5 * L * rpt + dv > most) most = 5 * L * rpt + dv;
+  }
+  return most;
+}
+
+template <int RPT>
+static int dr_launch(int L, dim3 grid, int threads, size_t smem, cudaStream_t s, const float* rec, const int* segs, float* state,
+                     float* out, int H, int dk, int dv, int cols, int chunk) {
+#define DR_LAUNCH(LL)                                                                                                       \
+  do {                                                                                                                      \
+    static HkSmemCache cache;                                                                                               \
+    int e = hk_allow_smem(delta_rule_scan_kernel<RPT, LL>, smem, cache);                                                    \
+    if (e) return e;                                                                                                        \
+    return hk_launch(delta_rule_scan_kernel<RPT, LL>, grid, dim3(threads), smem, s, rec, segs, state, out, H, dk, dv, cols, chunk); \
+  } while (0)
+  switch (L) {
+    case 1: DR_LAUNCH(1);
+    case 2: DR_LAUNCH(2);
+    case 4: DR_LAUNCH(4);
+    case 8: DR_LAUNCH(8);
+    case 16: DR_LAUNCH(16);
+    default: DR_LAUNCH(32);
+  }
+#undef DR_LAUNCH
+}
+
+// `rec`: scratch of n_rows * H * hk_delta_rule_record(dk, dv) floats (16-byte aligned) that the call fills and reads.
 HK_API int hk_delta_rule_scan(const float* r, const float* k, const float* v, const float* al, long long ld, const float* wl,
                               long long ldw, const float* a_bias, const float* w_bias, const int* segs, int n_seg, int n_rows,
                               float* rec, float* state, float* out, int H, int dk, int dv, float decay_scale, float key_eps,
                               void* stream) {
   if (n_seg <= 0 || n_rows <= 0) return 0;
-  if (H < 1 || dk < 1 || dv < 1 || dk > DR_MAX_RPT * 32 || ((uintptr_t)rec & 15)) return HK_ERR_UNSUPPORTED;
+  if (H < 1 || dk < 1 || dv < 1 || dk > 2048 || ((uintptr_t)rec & 15)) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
+  // lanes per column: one where requests x heads x columns alone give every SM four warps or more, else as many as that takes
+  const long long warps1 = ((long long)n_seg * H * dv + 31) / 32;
+  int spread = 1;
+  while (spread < 32 && warps1 * spread < 4 * 148) spread <<= 1;
+  int L, rpt;
+  dr_layout(dk, spread, &L, &rpt);
+  if (!rpt) return HK_ERR_UNSUPPORTED;
+  const int R = 5 * L * rpt + dv;
   {
     const long long items = (long long)n_rows * H;
     int e = hk_launch(delta_rule_prep_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, s, r, k, v, al, ld, wl, ldw, a_bias,
-                      w_bias, rec, items, H, dk, dv, decay_scale, key_eps);
+                      w_bias, rec, items, H, dk, dv, L, rpt, decay_scale, key_eps);
     if (e) return e;
   }
-  // lanes per column: the fewest that leave a thread at most 8 state rows while a block still has 64 threads or more
-  int L = 1;
-  while (L < 32 && (dk + L - 1) / L > 8) L <<= 1;
-  while (L < 32 && dv * L < 64) L <<= 1;
-  const int rpt = (dk + L - 1) / L;
-  // columns per block: few enough that one request's heads fill the SMs, many enough that a block is two warps or more
-  int cols = min(dv, 256 / L);
-  while (cols > 8 && cols * L > 64 && (long long)n_seg * H * ((dv + cols - 1) / cols) < 296) cols >>= 1;
-  if (cols < 1) cols = 1;
+  if (dv & 3) {
+    const int cols = max(1, min(dv, 128 / L));
+    const int threads = ((cols * L + 31) / 32) * 32;      // whole warps: the lanes of a column meet by shuffle
+    const size_t smem = (size_t)(threads * rpt + R) * sizeof(float);
+    static HkSmemCache cache;
+    int e = hk_allow_smem(delta_rule_scan_plain_kernel, smem, cache);
+    if (e) return e;
+    return hk_launch(delta_rule_scan_plain_kernel, dim3((unsigned)(n_seg * H), (unsigned)((dv + cols - 1) / cols)), dim3(threads), smem, s,
+                     (const float*)rec, segs, state, out, H, dk, dv, L, rpt, cols);
+  }
+  // a block takes as many columns as 256 threads hold: they share the records that the ring brings
+  const int cols = max(1, min(dv, 256 / L));
   const int threads = ((cols * L + 31) / 32) * 32;
-  const int R = 5 * dk + dv;
   int chunk = 16;
-  while (chunk > 2 && (size_t)2 * chunk * R * sizeof(float) > 96 * 1024) chunk >>= 1;
+  while (chunk > 2 && (size_t)2 * chunk * R * sizeof(float) > 64 * 1024) chunk >>= 1;
   const size_t smem = (size_t)2 * chunk * R * sizeof(float);
   dim3 grid((unsigned)(n_seg * H), (unsigned)((dv + cols - 1) / cols));
-#define DR_LAUNCH(RP)                                                                                                       \
-  do {                                                                                                                      \
-    static HkSmemCache cache;                                                                                               \
-    int e = hk_allow_smem(delta_rule_scan_kernel<RP>, smem, cache);                                                         \
-    if (e) return e;                                                                                                        \
-    return hk_launch(delta_rule_scan_kernel<RP>, grid, dim3(threads), smem, s, (const float*)rec, segs, state, out, H, dk, dv, \
-                     L, cols, chunk);                                                                                       \
-  } while (0)
-  if (rpt <= 1) DR_LAUNCH(1);
-  if (rpt <= 2) DR_LAUNCH(2);
-  if (rpt <= 4) DR_LAUNCH(4);
-  if (rpt <= 8) DR_LAUNCH(8);
-  if (rpt <= 16) DR_LAUNCH(16);
-  DR_LAUNCH(32);
-#undef DR_LAUNCH
+  if (rpt == 8) return dr_launch<8>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
+  if (rpt == 16) return dr_launch<16>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
+  if (rpt == 32) return dr_launch<32>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
+  return dr_launch<64>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
 }
 
 // ------------------------------------------------------------------ generalised delta rule: the output's gate
@@ -302,6 +367,18 @@ mingru_scan_kernel(const float* __restrict__ proj, long long ld, const float* __
   const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
   const float bz = (ok && z_bias) ? z_bias[c] : 0.f, bx = (ok && x_bias) ? x_bias[c] : 0.f;
   float S = (ok && tl == 0) ? state[(size_t)slot * W + c] : 0.f;
+  if (count == 1) {                              // a decoded token: nothing to stage, one lane per channel does it all
+    if (ok && tl == 0) {
+      const float* p = proj + (size_t)row0 * ld + c;
+      const float z = sigmoid_f(p[0] + bz);
+      const float x = p[W] + bx;
+      const float g = p[2 * (size_t)W];
+      S = fmaf(1.0f - z, S, z * (x >= 0.f ? x + 0.5f : sigmoid_f(x)));
+      out[(size_t)row0 * W + c] = from_f32<T>(S * (g * sigmoid_f(g)));
+      state[(size_t)slot * W + c] = S;
+    }
+    return;
+  }
   float zl[MG_PER], xl[MG_PER], gl[MG_PER];
   auto fetch = [&](int t0) {
 #pragma unroll

@@ -2,7 +2,7 @@
 //
 // Everything that depends on the router's choice stays on the device, so the launches of a step depend
 // on its number of rows alone (a decode step through it can be captured in a graph):
-//   1. route:   one warp per token takes the E router logits (float32 products of the token's vector with
+//   1. route:   one block per token takes the E router logits (float32 products of the token's vector with
 //               the router's rows, summed in a fixed order), picks the `top` largest (the lower index wins a
 //               tie) and gives them the softmax over the chosen logits as weights.
 //   2. sort:    one CTA counts the (token, choice) pairs per expert, lays the experts' rows out one after
@@ -22,20 +22,22 @@
 #define RT_BK 16
 
 // ------------------------------------------------------------------------------------ 1. route
+#define RK_WARPS 8
 template <typename T>
-__global__ void route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids,
-                                  float* __restrict__ weights, int n, int d, int E, int top) {
-  extern __shared__ float sm[];               // [warps][E]
+__global__ void __launch_bounds__(RK_WARPS * 32)
+route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ weights, int n,
+                  int d, int E, int top) {
+  extern __shared__ float sm[];               // [RK_WARPS][E] partial logits, then [E] logits
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const int t = blockIdx.x * (blockDim.x >> 5) + wid;
-  if (t >= n) return;
-  float* z = sm + (size_t)wid * E;
+  const int t = blockIdx.x;                   // a block per token: its warps share the token's vector
+  float* part = sm;
+  float* z = sm + (size_t)RK_WARPS * E;
   const T* xr = x + (size_t)t * d;
   for (int e0 = 0; e0 < E; e0 += 8) {          // eight experts per pass over the token's vector
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int i = lane; i < d; i += 32) {
+    for (int i = threadIdx.x; i < d; i += RK_WARPS * 32) {
       const float xv = to_f32<T>(xr[i]);
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -44,10 +46,18 @@ __global__ void route_topk_kernel(const T* __restrict__ x, const float* __restri
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float sum = warp_sum(acc[j]);
-      if (lane == 0 && e0 + j < E) z[e0 + j] = sum;
+      if (lane == 0 && e0 + j < E) part[(size_t)wid * E + e0 + j] = sum;
     }
   }
-  __syncwarp();
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += RK_WARPS * 32) {       // the warps' shares in warp order
+    float sum = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < RK_WARPS; ++wv) sum += part[(size_t)wv * E + e];
+    z[e] = sum;
+  }
+  __syncthreads();
+  if (wid != 0) return;
   float first = 0.f, mine = 0.f, total = 0.f;
   int mine_id = 0;
   for (int k = 0; k < top; ++k) {
@@ -89,14 +99,19 @@ HK_API int hk_route_topk(const void* x, int dtype, const float* w, int* ids, flo
                          void* stream) {
   if (n <= 0) return 0;
   if (E < 1 || top < 1 || top > E || top > 32 || E > 2048) return HK_ERR_UNSUPPORTED;
-  const int warps = 4;
-  const size_t smem = (size_t)warps * E * sizeof(float);
-  dim3 grid((unsigned)((n + warps - 1) / warps));
+  const size_t smem = (size_t)(RK_WARPS + 1) * E * sizeof(float);
+  dim3 grid((unsigned)n);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == HK_F32)
-    return hk_launch(route_topk_kernel<float>, grid, dim3(warps * 32), smem, s, (const float*)x, w, ids, weights, n, d, E, top);
-  if (dtype == HK_BF16)
-    return hk_launch(route_topk_kernel<bf16>, grid, dim3(warps * 32), smem, s, (const bf16*)x, w, ids, weights, n, d, E, top);
+  if (dtype == HK_F32) {
+    static HkSmemCache cache;
+    if (int e = hk_allow_smem(route_topk_kernel<float>, smem, cache)) return e;
+    return hk_launch(route_topk_kernel<float>, grid, dim3(RK_WARPS * 32), smem, s, (const float*)x, w, ids, weights, n, d, E, top);
+  }
+  if (dtype == HK_BF16) {
+    static HkSmemCache cache;
+    if (int e = hk_allow_smem(route_topk_kernel<bf16>, smem, cache)) return e;
+    return hk_launch(route_topk_kernel<bf16>, grid, dim3(RK_WARPS * 32), smem, s, (const bf16*)x, w, ids, weights, n, d, E, top);
+  }
   return HK_ERR_UNSUPPORTED;
 }
 

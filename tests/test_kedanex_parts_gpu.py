@@ -88,7 +88,8 @@ def schedules(lengths):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("d,H,dk,rank", [(40, 2, 16, 6), (24, 3, 8, 4), (72, 1, 64, 8), (48, 2, 40, 5), (32, 1, 136, 3)])
+@pytest.mark.parametrize("d,H,dk,rank", [(40, 2, 16, 6), (24, 3, 8, 4), (72, 1, 64, 8), (48, 2, 40, 5), (32, 1, 136, 3),
+                                         (24, 2, 6, 2), (16, 1, 260, 2), (32, 4, 32, 7)])
 def test_general_delta_rule_under_every_cut(dtype, d, H, dk, rank):
     from hk_b200.parts import GeneralDeltaRule
     part = GeneralDeltaRule(d, H, dk, "m.", norm_eps=1e-5, decay_rank=rank)
