@@ -41,7 +41,7 @@ class KedanexMixer:
     width: int = 0          # mingru: size of the recurrent state
     kv_heads: int = 0       # attention
     vdim: int = 0           # attention: value size (the first vdim dimensions of the projected key)
-    window: int = 0         # attention: mask.size
+    window: int = 0         # attention: mask.size (0: no window)
     rot_dims: int = 0       # attention: rot.dims (0: no rotation)
     rot_base: float = 10000.0
     scale: float = 1.0      # attention
@@ -60,7 +60,9 @@ class KedanexMixer:
         vdim = opt_int(raw, "vdim", dim)
         if vdim > dim:
             raise ConfigError(f"config.json {where}'vdim' = {vdim} exceeds 'dim' = {dim}: the values are the projected keys")
-        window = need_int(_need_dict(raw, "mask", where), "size")
+        window = 0                                   # no mask: every earlier position stays visible
+        if raw.get("mask") is not None:
+            window = need_int(_need_dict(raw, "mask", where), "size")
         rot = raw.get("rot")
         rot_dims, rot_base = 0, 10000.0
         if rot is not None:
@@ -80,8 +82,9 @@ class KedanexMixer:
             return {"dim": self.dim, "heads": self.heads, **({"decay_rank": self.decay_rank} if self.decay_rank else {})}
         if self.kind == "mingru":
             return {"width": self.width}
-        d = {"dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads, "mask": {"size": self.window},
-             "scale": self.scale, "vdim": self.vdim}
+        d = {"dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads, "scale": self.scale, "vdim": self.vdim}
+        if self.window:
+            d["mask"] = {"size": self.window}
         if self.rot_dims:
             d["rot"] = {"base": self.rot_base, "dims": self.rot_dims}
         return d

@@ -37,7 +37,7 @@ def build_kedanex(cfg: KedanexConfig, max_positions: int = 0) -> ModelSpec:
                     ropes[key] = RotaryEmbedding(m.rot_base, m.rot_dims, positions, pairing="half")
                 rope = ropes[key]
             mixer = GQAAttention(d, m.heads, m.kv_heads, m.dim, p + "mix.", qk_norm_eps=eps, position=rope,
-                                 window=m.window, scale=m.scale, qk_norm_after=True, qk_norm_weight=False,
+                                 window=m.window or None, scale=m.scale, qk_norm_after=True, qk_norm_weight=False,
                                  value_from_key=True, v_head_dim=m.vdim, sink=True,
                                  names={"q": "q", "k": "k", "o": "o"})
         ffn = ffn_norm = post_ffn = None

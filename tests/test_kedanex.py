@@ -20,6 +20,10 @@ def test_config_reads_its_own_keys_and_round_trips():
     att = cfg.layers[1].mixer
     assert (att.heads, att.kv_heads, att.dim, att.vdim, att.window, att.rot_dims, att.rot_base, att.scale) == (2, 2, 32, 24, 300, 32, 10000.0, 0.2)
     assert cfg.layers[3].weights_of == 2 and cfg.layers[2].mlp is None and cfg.layers[1].mlp.top == 2
+    raw = copy.deepcopy(M.CONFIGS["Y"])
+    del raw["layers"][1]["mixer"]["mask"], raw["layers"][1]["mixer"]["rot"], raw["layers"][1]["mixer"]["vdim"]
+    free = config_from_dict(raw).layers[1].mixer
+    assert (free.window, free.rot_dims, free.vdim) == (0, 0, 32) and config_from_dict(config_from_dict(raw).to_dict()).layers[1].mixer == free
     for breaker, text in [
         (lambda r: r["layers"][1]["mixer"].pop("scale"), "scale"),
         (lambda r: r["layers"][1].update(type="conv"), "type"),

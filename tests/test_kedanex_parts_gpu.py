@@ -295,7 +295,8 @@ def test_polynorm_feed_forward(dtype, d, F):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("d,F,E,top,n", [(40, 24, 3, 1, 50), (32, 16, 8, 2, 150), (24, 8, 5, 5, 7), (64, 40, 4, 3, 1), (48, 72, 6, 2, 300)])
+@pytest.mark.parametrize("d,F,E,top,n", [(40, 24, 3, 1, 50), (32, 16, 8, 2, 150), (24, 8, 5, 5, 7), (64, 40, 4, 3, 1), (48, 72, 6, 2, 300),
+                                         (40, 12, 3, 2, 33), (36, 20, 40, 4, 90), (128, 96, 1, 1, 70)])
 def test_routed_feed_forward(dtype, d, F, E, top, n):
     from hk_b200.parts import RoutedFeedForward
     part = RoutedFeedForward(d, F, E, top, "f.")
