@@ -194,7 +194,10 @@ def attention_part(d, H, G, hd, vd, window, rot_dims, scale, positions=512, base
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("d,H,G,hd,vd,window,rot", [(40, 4, 2, 16, 16, 7, 8), (24, 3, 3, 8, 4, 1000, 8), (48, 6, 1, 32, 32, 33, 0),
-                                                    (64, 2, 1, 64, 64, 20, 64), (40, 2, 2, 40, 24, 5, 12)])
+                                                    (64, 2, 1, 64, 64, 20, 64), (40, 2, 2, 40, 24, 5, 12),
+                                                    # every head size of the flash kernels, which take the bfloat16 steps
+                                                    (64, 2, 1, 128, 128, 40, 128), (48, 4, 1, 96, 96, 50, 96), (40, 4, 2, 48, 48, 9, 16),
+                                                    (64, 2, 2, 80, 80, 1000, 40), (64, 2, 1, 112, 112, 30, 112), (32, 8, 1, 16, 16, 1, 16)])
 def test_window_sink_attention_under_every_cut(dtype, d, H, G, hd, vd, window, rot):
     part, mixer = attention_part(d, H, G, hd, vd, window, rot, scale=0.4)
     prec, w = bind_random(part, dtype, std=0.3)
