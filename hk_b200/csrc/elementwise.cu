@@ -524,8 +524,66 @@ __global__ void rms_norm_add_kernel(const float* __restrict__ y, const float* __
   for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] += src[i] * inv * w[i];
 }
 
+// The same for widths that are a multiple of 4 and at most 4 * PER * 256: the row is read once with 16-byte loads that
+// are all in flight together and stays in registers between the two passes (as `rms_norm_vec_kernel`).
+template <int PER>
+__global__ void __launch_bounds__(256)
+rms_norm_add_vec_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ residual, int d, float eps) {
+  __shared__ float warp_part[8];
+  __shared__ float inv_s;
+  const int r = blockIdx.x;
+  const int chunks = d >> 2;
+  const float4* src = reinterpret_cast<const float4*>(y + (size_t)r * d);
+  const float4* wv = reinterpret_cast<const float4*>(w);
+  float4* dst = reinterpret_cast<float4*>(residual + (size_t)r * d);
+  float4 v[PER], g[PER], x[PER];
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int c = threadIdx.x + k * 256;
+    const bool in = c < chunks;
+    v[k] = in ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    g[k] = in ? wv[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    x[k] = in ? dst[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    ss = fmaf(v[k].x, v[k].x, ss);
+    ss = fmaf(v[k].y, v[k].y, ss);
+    ss = fmaf(v[k].z, v[k].z, ss);
+    ss = fmaf(v[k].w, v[k].w, ss);
+  }
+  ss = warp_sum(ss);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) warp_part[wid] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += warp_part[i];
+    inv_s = 1.0f / sqrtf(tot / (float)d + eps);
+  }
+  __syncthreads();
+  const float inv = inv_s;
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int c = threadIdx.x + k * 256;
+    if (c < chunks)
+      dst[c] = make_float4(x[k].x + v[k].x * inv * g[k].x, x[k].y + v[k].y * inv * g[k].y, x[k].z + v[k].z * inv * g[k].z,
+                           x[k].w + v[k].w * inv * g[k].w);
+  }
+}
+
 HK_API int hk_rms_norm_add(const float* y, const float* w, float* residual, int n, int d, float eps, void* stream) {
   if (n <= 0) return 0;
+  if ((d & 3) == 0 && d >= 512 && (((uintptr_t)y | (uintptr_t)w | (uintptr_t)residual) & 15) == 0) {
+    const int chunks = d >> 2;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (chunks <= 256) return hk_launch(rms_norm_add_vec_kernel<1>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps);
+    if (chunks <= 2 * 256) return hk_launch(rms_norm_add_vec_kernel<2>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps);
+    if (chunks <= 4 * 256) return hk_launch(rms_norm_add_vec_kernel<4>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps);
+    if (chunks <= 8 * 256) return hk_launch(rms_norm_add_vec_kernel<8>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps);
+  }
   return hk_launch(rms_norm_add_kernel, dim3((unsigned)n), dim3(d >= 2048 ? 256 : 128), 0, (cudaStream_t)stream, y, w, residual, d,
                    eps);
 }
@@ -572,9 +630,90 @@ __global__ void polynorm_kernel(const float* __restrict__ z, const float* __rest
   }
 }
 
+// The same for F a multiple of 4 and at most 4 * PER * 256, the row in registers between the two passes.
+template <typename TO, int PER>
+__global__ void __launch_bounds__(256)
+polynorm_vec_kernel(const float* __restrict__ z, const float* __restrict__ coef, TO* __restrict__ out, int F, float eps) {
+  __shared__ float part[3][8];
+  __shared__ float inv_s[3];
+  const int r = blockIdx.x;
+  const int chunks = F >> 2;
+  const float4* src = reinterpret_cast<const float4*>(z + (size_t)r * F);
+  float4 v[PER];
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int c = threadIdx.x + k * 256;
+    v[k] = c < chunks ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = e[i], a2 = a * a, a3 = a2 * a;
+      s1 = fmaf(a, a, s1);
+      s2 = fmaf(a2, a2, s2);
+      s3 = fmaf(a3, a3, s3);
+    }
+  }
+  s1 = warp_sum(s1);
+  s2 = warp_sum(s2);
+  s3 = warp_sum(s3);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) {
+    part[0][wid] = s1;
+    part[1][wid] = s2;
+    part[2][wid] = s3;
+  }
+  __syncthreads();
+  if (threadIdx.x < 3) {
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += part[threadIdx.x][i];
+    inv_s[threadIdx.x] = 1.0f / sqrtf(tot / (float)F + eps);
+  }
+  __syncthreads();
+  const float a = coef[0] * inv_s[0], b = coef[1] * inv_s[1], c3 = coef[2] * inv_s[2], e0 = coef[3];
+  TO* dst = out + (size_t)r * F;
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int c = threadIdx.x + k * 256;
+    if (c >= chunks) continue;
+    const float in[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+    float o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float x = in[i], x2 = x * x;
+      o[i] = a * x + b * x2 + c3 * (x2 * x) + e0;
+    }
+    if (sizeof(TO) == 4) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + 4 * c) = make_float4(o[0], o[1], o[2], o[3]);
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+      *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(dst) + 4 * c) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+  }
+}
+
+template <typename TO>
+static int polynorm_vec(const float* z, const float* coef, TO* out, int n, int F, float eps, cudaStream_t s) {
+  const int chunks = F >> 2;
+  if (chunks <= 2 * 256) return hk_launch(polynorm_vec_kernel<TO, 2>, dim3((unsigned)n), dim3(256), 0, s, z, coef, out, F, eps);
+  if (chunks <= 4 * 256) return hk_launch(polynorm_vec_kernel<TO, 4>, dim3((unsigned)n), dim3(256), 0, s, z, coef, out, F, eps);
+  if (chunks <= 8 * 256) return hk_launch(polynorm_vec_kernel<TO, 8>, dim3((unsigned)n), dim3(256), 0, s, z, coef, out, F, eps);
+  return hk_launch(polynorm_vec_kernel<TO, 16>, dim3((unsigned)n), dim3(256), 0, s, z, coef, out, F, eps);
+}
+
 HK_API int hk_polynorm(const float* z, const float* coef, void* out, int out_dtype, int n, int F, float eps, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  if ((F & 3) == 0 && F >= 512 && F <= 4 * 16 * 256 && (((uintptr_t)z | (uintptr_t)out) & 15) == 0) {
+    if (out_dtype == HK_F32) return polynorm_vec<float>(z, coef, (float*)out, n, F, eps, s);
+    if (out_dtype == HK_BF16) return polynorm_vec<bf16>(z, coef, (bf16*)out, n, F, eps, s);
+    return HK_ERR_UNSUPPORTED;
+  }
   const int threads = F >= 2048 ? 256 : 128;
   if (out_dtype == HK_F32) return hk_launch(polynorm_kernel<float>, dim3((unsigned)n), dim3(threads), 0, s, z, coef, (float*)out, F, eps);
   if (out_dtype == HK_BF16) return hk_launch(polynorm_kernel<bf16>, dim3((unsigned)n), dim3(threads), 0, s, z, coef, (bf16*)out, F, eps);

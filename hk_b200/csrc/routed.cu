@@ -37,11 +37,24 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __r
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int i = threadIdx.x; i < d; i += RK_WARPS * 32) {
-      const float xv = to_f32<T>(xr[i]);
+    if ((d & 3) == 0 && (((uintptr_t)w | (uintptr_t)xr) & 15) == 0) {
+      // four consecutive elements a thread: 16-byte reads of the router's rows, all eight experts' in flight together
+      for (int i = threadIdx.x * 4; i < d; i += RK_WARPS * 32 * 4) {
+        const float x0 = to_f32<T>(xr[i]), x1 = to_f32<T>(xr[i + 1]), x2 = to_f32<T>(xr[i + 2]), x3 = to_f32<T>(xr[i + 3]);
+        float4 wv[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (e0 + j < E) acc[j] = fmaf(xv, w[(size_t)(e0 + j) * d + i], acc[j]);
+        for (int j = 0; j < 8; ++j)
+          wv[j] = e0 + j < E ? *reinterpret_cast<const float4*>(w + (size_t)(e0 + j) * d + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = fmaf(x3, wv[j].w, fmaf(x2, wv[j].z, fmaf(x1, wv[j].y, fmaf(x0, wv[j].x, acc[j]))));
+      }
+    } else {
+      for (int i = threadIdx.x; i < d; i += RK_WARPS * 32) {
+        const float xv = to_f32<T>(xr[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (e0 + j < E) acc[j] = fmaf(xv, w[(size_t)(e0 + j) * d + i], acc[j]);
+      }
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {

@@ -343,3 +343,42 @@ def test_sandwich_norm_block(dtype, with_ffn):
         h = K.rms_norm(want, w["n2"], eps)
         want = want + K.rms_norm(K.polynorm_ff(h, w, "f.", eps), w["n2b"], eps)
     close(x.double().cpu().numpy(), want, dtype)
+
+
+@pytest.mark.parametrize("d", [40, 512, 1000, 4096, 5000, 8200])
+def test_rms_norm_add_kernel_over_widths(d):
+    """Narrow rows, rows that stay in registers (one to eight 16-byte loads a thread) and rows too wide for that."""
+    from hk_b200.csrc import ops
+    y = torch.randn(5, d, device="cuda") * 3.0
+    w = 1.0 + 0.2 * torch.randn(d, device="cuda")
+    res = torch.randn(5, d, device="cuda")
+    want = res.double() + y.double() / torch.sqrt((y.double() ** 2).mean(-1, keepdim=True) + 1e-5) * w.double()
+    ops.rms_norm_add(y, w, 1e-5, res)
+    close(res.double().cpu().numpy(), want.cpu().numpy(), torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("F", [36, 512, 3000, 12288, 16384, 20000])
+def test_polynorm_kernel_over_widths(dtype, F):
+    from hk_b200.csrc import ops
+    z = torch.randn(3, F, device="cuda") * 1.5
+    coef = torch.tensor([0.7, -0.4, 0.25, 0.1], device="cuda")
+    out = torch.empty(3, F, dtype=dtype, device="cuda")
+    ops.polynorm(z, coef, 1e-5, out)
+    zd = z.double().cpu().numpy()
+    want = 0.7 * K.unit_rms(zd, 1e-5) - 0.4 * K.unit_rms(zd ** 2, 1e-5) + 0.25 * K.unit_rms(zd ** 3, 1e-5) + 0.1
+    close(out.double().cpu().numpy(), want, dtype)
+
+
+@pytest.mark.parametrize("d,E,top", [(4096, 8, 2), (1000, 20, 3), (72, 5, 5)])
+def test_router_over_widths(d, E, top):
+    from hk_b200.csrc import ops
+    x = torch.randn(9, d, device="cuda").to(torch.bfloat16)
+    w = torch.randn(E, d, device="cuda") * 0.1
+    ids = torch.empty(9, top, dtype=torch.int32, device="cuda")
+    wts = torch.empty(9, top, device="cuda")
+    ops.route_topk(x, w, ids, wts)
+    z = x.double() @ w.double().T
+    best = torch.topk(z, top, dim=1)
+    assert torch.equal(ids.long().cpu(), best.indices.cpu())
+    np.testing.assert_allclose(wts.double().cpu().numpy(), torch.softmax(best.values, dim=1).cpu().numpy(), rtol=1e-4, atol=1e-6)
