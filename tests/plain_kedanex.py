@@ -23,10 +23,6 @@ def silu(x):
     return x * sigmoid(x)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 round_inputs = None      # a function, to model an implementation that narrows the inputs of its matrix products
 
 
