@@ -245,3 +245,24 @@ def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None) -> bool:
         return False
     ops._check(code, "gemm+swiglu (tcgen05)")
     return True
+
+
+GROUPED_ROWS = 128      # rows of a tile of the grouped tcgen05 product: an expert's rows start on a multiple of it
+
+
+def run_grouped(a, w, out, groups, gated: bool) -> bool:
+    """out[tile rows] = a[tile rows] w[groups[tile]]^T over tiles of 128 rows (`hk_gemm_tc_grouped`)."""
+    from . import ops
+    M, K = a.shape
+    E, N = int(w.shape[0]), int(w.shape[1])
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or K % 8 or M % GROUPED_ROWS or not _aligned(a, w) \
+            or not w.is_contiguous() or (gated and N % 2):
+        return False
+    bn = min(256, -(-N // 32) * 32)
+    lib = build.load("gemm_tc")
+    code = lib.hk_gemm_tc_grouped(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), 2 if gated else 0, bn, E,
+                                  _ptr(groups), _ptr(status_flag(a.device)), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    ops._check(code, "grouped gemm (tcgen05)")
+    return True

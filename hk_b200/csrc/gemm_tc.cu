@@ -230,7 +230,7 @@ template <int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
                int M, int N, int K, long long ldo, int bn, int stages, int splits, float* __restrict__ partial,
-               int* __restrict__ status) {
+               int* __restrict__ status, const int* __restrict__ groups) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   Control& sm = *reinterpret_cast<Control*>(base);
@@ -281,6 +281,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int mn = tile % mn_tiles, ks = tile / mn_tiles;
         const int m0 = (mn % m_tiles) * BM, nt = mn / m_tiles;
+        // grouped: the rows of a 128-row tile all belong to one group, whose weights are rows g N .. of w; a tile
+        // without a group (-1) is skipped, by every role alike
+        const int g = groups ? groups[mn % m_tiles] : 0;
+        if (g < 0) continue;
+        const int w0 = g * N;
         const int kb0 = (int)((long long)k_blocks_all * ks / splits), kb1 = (int)((long long)k_blocks_all * (ks + 1) / splits);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&sm.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -288,10 +293,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           mbar_expect_tx(&sm.full[stage], tx_bytes);
           tma_load_2d(st, &map_a, &sm.full[stage], kb * BK, m0);
           if (EPI == EPI_SWIGLU) {
-            tma_load_2d(st + A_BYTES, &map_w, &sm.full[stage], kb * BK, nt * h);
-            tma_load_2d(st + A_BYTES + h * (BK * 2), &map_w, &sm.full[stage], kb * BK, F + nt * h);
+            tma_load_2d(st + A_BYTES, &map_w, &sm.full[stage], kb * BK, w0 + nt * h);
+            tma_load_2d(st + A_BYTES + h * (BK * 2), &map_w, &sm.full[stage], kb * BK, w0 + F + nt * h);
           } else {
-            tma_load_2d(st + A_BYTES, &map_w, &sm.full[stage], kb * BK, nt * bn);
+            tma_load_2d(st + A_BYTES, &map_w, &sm.full[stage], kb * BK, w0 + nt * bn);
           }
           if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
@@ -307,9 +312,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (groups && groups[(tile % mn_tiles) % m_tiles] < 0) continue;     // a skipped tile takes no accumulator buffer
         const int buf = local & 1;
         const uint32_t use = (uint32_t)(local >> 1);
+        ++local;
         if (!mbar_wait(&sm.tmem_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * MAX_BN);
@@ -337,9 +344,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int quarter = warp & 3;                     // the TMEM lanes this warp may read: 32*quarter ..
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      if (groups && groups[(tile % mn_tiles) % m_tiles] < 0) continue;
       const int buf = local & 1;
       const uint32_t use = (uint32_t)(local >> 1);
+      ++local;
       const int mn = tile % mn_tiles, ks = tile / mn_tiles;
       const int m0 = (mn % m_tiles) * BM, nt = mn / m_tiles;
       const int row = m0 + quarter * 32 + lane;
@@ -515,7 +524,7 @@ __global__ void splitk_reduce_vec_kernel(const float* __restrict__ partial, floa
 
 template <int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int bn, int splits,
-           float* partial, int* status, cudaStream_t s) {
+           float* partial, int* status, cudaStream_t s, const int* groups = nullptr) {
   static HkSmemCache allowed = {};
   const uint32_t stage_bytes = stage_bytes_of(bn);
   int stages = RING_BYTES / (int)stage_bytes;
@@ -526,7 +535,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
   const int tiles = ((M + BM - 1) / BM) * n_tiles * splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   // dependent launches (measured over decode steps of 24 and 64 rows: 1 % faster; the kernels after this one set up while it drains)
-  int code = hk_launch_pdl(gemm_tc_kernel<EPI>, dim3(grid), dim3(NUM_THREADS), smem, s, ma, mw, out, M, N, K, ldo, bn, stages, splits, partial, status);
+  int code = hk_launch_pdl(gemm_tc_kernel<EPI>, dim3(grid), dim3(NUM_THREADS), smem, s, ma, mw, out, M, N, K, ldo, bn, stages, splits, partial, status, groups);
   if (code != 0 || splits <= 1) return code;
   if (EPI != EPI_SWIGLU && (N & 3) == 0 && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0) {
     const long long quads = (long long)M * (N / 4);
@@ -567,3 +576,21 @@ HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int
 
 // Floats of scratch that `hk_gemm_tc` needs for `splits` K slices.
 HK_API long long hk_gemm_tc_partial_floats(int M, int N, int splits) { return (long long)(slice_floats(M, N) * (size_t)splits); }
+
+// The grouped form: a has M rows in tiles of 128 that each belong to one group (groups[tile] = its index, -1: skip the
+// tile), w is [n_groups][N][K] and out has a's rows: out[tile rows] = a[tile rows] w[group]^T.  Epilogue 0 (fp32 store)
+// or 2 (silu(gate) * up, w[group] = [N/2 gate rows | N/2 up rows], out bf16 [M, N/2]).  No K slices.
+HK_API int hk_gemm_tc_grouped(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int bn,
+                              int n_groups, const int* groups, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || n_groups <= 0) return 0;
+  if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || (M % BM) || groups == nullptr) return HK_ERR_UNSUPPORTED;
+  if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return HK_ERR_UNSUPPORTED;
+  if (bn < 16 || bn > MAX_BN || (bn & 15)) return HK_ERR_UNSUPPORTED;
+  if (epilogue == EPI_SWIGLU && ((N & 1) || (bn & 31))) return HK_ERR_UNSUPPORTED;
+  if ((long long)n_groups * N > 0x7fffffffLL) return HK_ERR_UNSUPPORTED;
+  CUtensorMap ma, mw;
+  if (!make_map(&ma, a, M, K, BM) || !make_map(&mw, w, n_groups * N, K, epilogue == EPI_SWIGLU ? bn / 2 : bn)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (epilogue == EPI_STORE) return launch<EPI_STORE>(ma, mw, out, M, N, K, ldo, bn, 1, nullptr, status, s, groups);
+  return launch<EPI_SWIGLU>(ma, mw, out, M, N, K, ldo, bn, 1, nullptr, status, s, groups);
+}

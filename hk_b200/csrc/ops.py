@@ -565,8 +565,41 @@ def route_combine(ys, inv, weights, y, accumulate: bool = False) -> None:
     _need(weights, "weights", torch.float32, 2)
     _need(y, "y", torch.float32, 2)
     n, top = weights.shape
-    if y.shape[0] != n or ys.shape[1] != y.shape[1] or inv.numel() != n * top or ys.shape[0] != n * top:
+    if y.shape[0] != n or ys.shape[1] != y.shape[1] or inv.numel() != n * top or ys.shape[0] < n * top:
         raise KernelError("route_combine: shapes do not fit")
     lib = build.load("routed")
     _check(lib.hk_route_combine(_ptr(ys), _ptr(inv), _ptr(weights), _ptr(y), n, y.shape[1], top, 1 if accumulate else 0,
                                 _stream()), "route_combine")
+
+
+def route_sort_padded(ids, n_experts: int, pad: int, perm, inv, groups) -> None:
+    """The layout for the tcgen05 grouped product: every expert's rows start on a multiple of `pad`.  perm int32 [M_max]
+    (sorted place -> pair, -1 for padding), inv [pairs], groups [M_max / pad] (tile -> expert or -1);
+    M_max >= pairs + E * (pad - 1) and a multiple of pad."""
+    for name, t in (("ids", ids), ("perm", perm), ("inv", inv), ("groups", groups)):
+        _need(t, name, torch.int32)
+    pairs, m_max = ids.numel(), perm.numel()
+    if inv.numel() != pairs or groups.numel() * pad != m_max:
+        raise KernelError("route_sort_padded: shapes do not fit")
+    lib = build.load("routed")
+    _check(lib.hk_route_sort_padded(_ptr(ids), pairs, n_experts, int(pad), _ptr(perm), _ptr(inv), _ptr(groups), m_max, _stream()),
+           "route_sort_padded")
+
+
+def route_gather(x, perm, top: int, xs) -> None:
+    """xs[p, :] = x[perm[p] // top, :] (zeros where perm[p] < 0), bfloat16 rows of a multiple of 8 elements."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(xs, "xs", torch.bfloat16, 2)
+    _need(perm, "perm", torch.int32, 1)
+    if xs.shape[0] != perm.shape[0] or xs.shape[1] != x.shape[1]:
+        raise KernelError("route_gather: shapes do not fit")
+    lib = build.load("routed")
+    _check(lib.hk_route_gather(_ptr(x), _ptr(perm), int(top), _ptr(xs), xs.shape[0], xs.shape[1], _stream()), "route_gather")
+
+
+def grouped_gemm_tc(a, w, out, groups, gated: bool) -> bool:
+    """The grouped product on the tcgen05 kernel: a bf16 [M, K] in tiles of 128 rows, tile t belonging to expert groups[t]
+    (-1: skipped); w bf16 [E, N, K] (gated: [E, 2N, K]); out float32 [M, N], or bf16 silu(gate) * up when gated.  False when
+    the kernel refuses the shape."""
+    from . import gemm_fast
+    return gemm_fast.run_grouped(a, w, out, groups, gated)

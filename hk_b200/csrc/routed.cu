@@ -176,6 +176,63 @@ HK_API int hk_route_sort(const int* ids, int pairs, int E, int* offsets, int* pe
 
 HK_API int hk_route_tile_rows() { return RT_BM; }
 
+// The padded layout for the tcgen05 grouped product: every expert's rows start on a multiple of `pad` (the product's
+// 128-row tile), so a tile's rows all belong to one expert.  perm[M_max] (sorted place -> pair, -1 for padding),
+// inv[pairs] (pair -> sorted place), groups[M_max / pad] (tile -> expert, -1 for tiles past the last expert).
+__global__ void __launch_bounds__(1024)
+route_sort_padded_kernel(const int* __restrict__ ids, int pairs, int E, int pad, int* __restrict__ perm, int* __restrict__ inv,
+                         int* __restrict__ groups, int m_max) {
+  extern __shared__ int smi[];                // counts[E], cursor[E]
+  int* counts = smi;
+  int* cursor = smi + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  for (int p = threadIdx.x; p < m_max; p += blockDim.x) perm[p] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&counts[ids[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      cursor[e] = at;
+      const int span = (counts[e] + pad - 1) / pad * pad;
+      for (int r = 0; r < span && at + r < m_max; r += pad) groups[(at + r) / pad] = e;
+      at += span;
+    }
+    for (int t = at / pad; t < m_max / pad; ++t) groups[t] = -1;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int at = atomicAdd(&cursor[ids[p]], 1);
+    perm[at] = p;
+    inv[p] = at;
+  }
+}
+
+HK_API int hk_route_sort_padded(const int* ids, int pairs, int E, int pad, int* perm, int* inv, int* groups, int m_max, void* stream) {
+  if (pairs <= 0) return 0;
+  if (E > 4096 || pad < 1 || m_max % pad || m_max < pairs + E * (pad - 1)) return HK_ERR_UNSUPPORTED;
+  return hk_launch(route_sort_padded_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), (cudaStream_t)stream, ids, pairs, E, pad,
+                   perm, inv, groups, m_max);
+}
+
+// xs[p, :] = x[perm[p] / top, :], or zeros where perm[p] < 0: the tokens' vectors in the padded sorted order (bf16, d % 8 == 0).
+__global__ void route_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ perm, int top, bf16* __restrict__ xs, int d) {
+  const int p = blockIdx.x;
+  const int src = perm[p];
+  uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)p * d);
+  const uint4* from = reinterpret_cast<const uint4*>(x + (size_t)(src < 0 ? 0 : src / top) * d);
+  for (int i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src < 0 ? make_uint4(0, 0, 0, 0) : from[i];
+}
+
+HK_API int hk_route_gather(const void* x, const int* perm, int top, void* xs, int m_max, int d, void* stream) {
+  if (m_max <= 0) return 0;
+  if ((d & 7) || (((uintptr_t)x | (uintptr_t)xs) & 15)) return HK_ERR_UNSUPPORTED;
+  return hk_launch(route_gather_kernel, dim3((unsigned)m_max), dim3(d >= 2048 ? 256 : 128), 0, (cudaStream_t)stream, (const bf16*)x, perm,
+                   top, (bf16*)xs, d);
+}
+
+
+
 // ------------------------------------------------------------------------------------ 3. experts
 // out rows are sorted places.  GATED: w is [E][2N][K] = N gate rows then N up rows per expert, out[p, n] (type TO) =
 // silu(gate) * up.  Otherwise w is [E][N][K] and out[p, n] (float) = a[p] . w[e][n].  `gather`: row p of `a` is row

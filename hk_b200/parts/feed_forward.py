@@ -120,6 +120,30 @@ class RoutedFeedForward(Part):
         self.w_down = torch.stack([tensors[self._expert(e, "down")].to(dt) for e in range(self.E)]).contiguous()
         self._tile_rows = ops.route_tile_rows()
 
+    TC_MIN_PAIRS = 1024     # from this many (row, choice) pairs on, a bfloat16 step takes the tcgen05 grouped product
+
+    def _forward_tc(self, xb, residual, ids, weights, accumulate: bool) -> bool:
+        """Prompt-sized steps in bfloat16: the rows are gathered into expert order with every expert's rows padded to whole
+        128-row tiles, and both products run on the tcgen05 kernel with a tile's expert choosing its weights."""
+        from ..csrc import gemm_fast
+        n, dev = xb.shape[0], xb.device
+        pairs, pad = n * self.top, gemm_fast.GROUPED_ROWS
+        m_max = -(-(pairs + self.E * (pad - 1)) // pad) * pad
+        perm = torch.empty(m_max, dtype=torch.int32, device=dev)
+        inv = torch.empty(pairs, dtype=torch.int32, device=dev)
+        groups = torch.empty(m_max // pad, dtype=torch.int32, device=dev)
+        ops.route_sort_padded(ids, self.E, pad, perm, inv, groups)
+        xs = torch.empty((m_max, self.hidden), dtype=xb.dtype, device=dev)
+        ops.route_gather(xb, perm, self.top, xs)
+        h = torch.empty((m_max, self.F), dtype=xb.dtype, device=dev)
+        if not ops.grouped_gemm_tc(xs, self.w_gate_up, h, groups, gated=True):
+            return False
+        ys = torch.empty((m_max, self.hidden), dtype=torch.float32, device=dev)
+        if not ops.grouped_gemm_tc(h, self.w_down, ys, groups, gated=False):
+            return False
+        ops.route_combine(ys, inv, weights, residual, accumulate=accumulate)
+        return True
+
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, accumulate: bool = True) -> None:
         n, dev = xb.shape[0], xb.device
         pairs = n * self.top
@@ -128,6 +152,9 @@ class RoutedFeedForward(Part):
         ops.route_topk(xb, self.w_router, ids, weights)
         if RoutedFeedForward.route_log is not None:
             RoutedFeedForward.route_log.append(ids.clone())
+        if xb.dtype == torch.bfloat16 and pairs >= self.TC_MIN_PAIRS and self.hidden % 8 == 0 and self.F % 8 == 0 \
+                and self._forward_tc(xb, residual, ids, weights, accumulate):
+            return
         max_tiles = pairs // self._tile_rows + min(self.E, pairs)
         offsets = torch.empty(self.E + 1, dtype=torch.int32, device=dev)
         perm = torch.empty(pairs, dtype=torch.int32, device=dev)
