@@ -223,11 +223,32 @@ def kernel_points(width: int, n: int, peaks: dict) -> dict:
     ys = torch.empty(pairs, width, device=dev)
     used = min(E, pairs)
     us = _time_kernel(lambda: ops.grouped_gemm(xb, wgu, h, tiles, offsets, perm, top, gather=True, gated=True))
-    note("grouped gate/up product + SwiGLU", us, used * 2 * Fe * width * 2 + n * width * 2 + pairs * Fe * 2, 2.0 * pairs * 2 * Fe * width, tc,
+    note("grouped gate/up product + SwiGLU (mma.sync)", us, used * 2 * Fe * width * 2 + n * width * 2 + pairs * Fe * 2, 2.0 * pairs * 2 * Fe * width, tc,
          like="gate/up product with SwiGLU epilogue (same FLOPs)")
     us = _time_kernel(lambda: ops.grouped_gemm(h, wd, ys, tiles, offsets, perm, top, gather=False, gated=False))
-    note("grouped down product", us, used * Fe * width * 2 + pairs * (Fe * 2 + width * 4), 2.0 * pairs * Fe * width, tc,
+    note("grouped down product (mma.sync)", us, used * Fe * width * 2 + pairs * (Fe * 2 + width * 4), 2.0 * pairs * Fe * width, tc,
          like="down product (same FLOPs)")
+    if pairs >= 1024:
+        # the form that prompt-sized steps take: rows gathered into padded expert order, both products on the tcgen05 kernel
+        from .csrc import gemm_fast
+        pad = gemm_fast.GROUPED_ROWS
+        m_max = -(-(pairs + E * (pad - 1)) // pad) * pad
+        perm_p = torch.empty(m_max, dtype=torch.int32, device=dev)
+        inv_p = torch.empty(pairs, dtype=torch.int32, device=dev)
+        groups = torch.empty(m_max // pad, dtype=torch.int32, device=dev)
+        us = _time_kernel(lambda: ops.route_sort_padded(ids, E, pad, perm_p, inv_p, groups))
+        note("route_sort_padded", us, pairs * 16, 0, 0)
+        xs = torch.empty(m_max, width, dtype=torch.bfloat16, device=dev)
+        us = _time_kernel(lambda: ops.route_gather(xb, perm_p, top, xs))
+        note("route_gather", us, (n + m_max) * width * 2, 0, 0)
+        hp = torch.empty(m_max, Fe, dtype=torch.bfloat16, device=dev)
+        ysp = torch.empty(m_max, width, device=dev)
+        us = _time_kernel(lambda: ops.grouped_gemm_tc(xs, wgu, hp, groups, gated=True))
+        note("grouped gate/up product + SwiGLU (tcgen05)", us, used * 2 * Fe * width * 2 + pairs * (width + Fe) * 2, 2.0 * pairs * 2 * Fe * width, tc,
+             like="gate/up product with SwiGLU epilogue (same FLOPs)")
+        us = _time_kernel(lambda: ops.grouped_gemm_tc(hp, wd, ysp, groups, gated=False))
+        note("grouped down product (tcgen05)", us, used * Fe * width * 2 + pairs * (Fe * 2 + width * 4), 2.0 * pairs * Fe * width, tc,
+             like="down product (same FLOPs)")
     y = torch.empty(n, width, device=dev)
     us = _time_kernel(lambda: ops.route_combine(ys, inv, wts, y))
     note("route_combine", us, pairs * width * 4 + n * width * 4, 0, 0)
