@@ -294,8 +294,11 @@ HK_API int hk_delta_rule_scan(const float* r, const float* k, const float* v, co
     return hk_launch(delta_rule_scan_plain_kernel, dim3((unsigned)(n_seg * H), (unsigned)((dv + cols - 1) / cols)), dim3(threads), smem, s,
                      (const float*)rec, segs, state, out, H, dk, dv, L, rpt, cols);
   }
-  // a block takes as many columns as 256 threads hold: they share the records that the ring brings
-  const int cols = max(1, min(dv, 256 / L));
+  // a block takes as many columns as 256 threads hold (they share the records that the ring brings), fewer while the
+  // blocks do not yet fill the SMs twice: one request of 2,048 tokens at 32 heads of 64 runs 808 us with 8 columns a
+  // block (256 blocks of 64 threads) against 1,096 with 32 and 839 with 4; below 4 every block fetches too much
+  int cols = max(1, min(dv, 256 / L));
+  while (cols > 8 && cols * L > 64 && (long long)n_seg * H * ((dv + cols - 1) / cols) < 2 * 148) cols >>= 1;
   const int threads = ((cols * L + 31) / 32) * 32;
   int chunk = 16;
   while (chunk > 2 && (size_t)2 * chunk * R * sizeof(float) > 64 * 1024) chunk >>= 1;
