@@ -78,7 +78,7 @@ __device__ __forceinline__ void dr_cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <int RPT, int L>
+template <int RPT, int L, int CPT>     // CPT: columns a lane group owns (they share every load of the token's vectors)
 __global__ void __launch_bounds__(256)
 delta_rule_scan_kernel(const float* __restrict__ rec, const int* __restrict__ segs, float* __restrict__ state,
                        float* __restrict__ out, int H, int dk, int dv, int cols, int chunk) {
@@ -89,14 +89,20 @@ delta_rule_scan_kernel(const float* __restrict__ rec, const int* __restrict__ se
   const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
   const int col0 = blockIdx.y * cols;
   const int tid = threadIdx.x;
-  const int sub = tid % L, cidx = tid / L, col = col0 + cidx;
-  const bool col_ok = cidx < cols && col < dv;
-  float S[RPT];
+  const int sub = tid % L, cidx = (tid / L) * CPT;           // first of this lane group's columns, within the block
+  bool col_ok[CPT];
+  int col[CPT];
+  float S[CPT][RPT];
   float* sp = state + ((size_t)slot * H + h) * dk * dv;
 #pragma unroll
-  for (int m = 0; m < RPT; ++m) {
-    const int i = sub + L * m;
-    S[m] = (col_ok && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
+  for (int c = 0; c < CPT; ++c) {
+    col[c] = col0 + cidx + c;
+    col_ok[c] = cidx + c < cols && col[c] < dv;
+#pragma unroll
+    for (int m = 0; m < RPT; ++m) {
+      const int i = sub + L * m;
+      S[c][m] = (col_ok[c] && i < dk) ? sp[(size_t)i * dv + col[c]] : 0.f;
+    }
   }
   const int pieces = R >> 2;                    // records are whole 16-byte pieces: P is a multiple of 8, dv of 4
   auto fetch = [&](int c) {                     // chunk c -> stage c & 1
@@ -108,10 +114,10 @@ delta_rule_scan_kernel(const float* __restrict__ rec, const int* __restrict__ se
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   const int nchunks = (count + chunk - 1) / chunk;
-  float* op = out + (size_t)row0 * H * dv + (size_t)h * dv + col;
+  float* op = out + (size_t)row0 * H * dv + (size_t)h * dv + col[0];
   const size_t ostep = (size_t)H * dv;
-  const bool writer = col_ok && sub == 0;
-  const int mine = sub * RPT, vat = 5 * P + min(col, dv - 1);
+  const bool lead = sub == 0;
+  const int mine = sub * RPT, vat = 5 * P + min(col[0], dv - CPT);
   fetch(0);
   for (int c = 0; c < nchunks; ++c) {
     if (c + 1 < nchunks) {
@@ -127,48 +133,69 @@ delta_rule_scan_kernel(const float* __restrict__ rec, const int* __restrict__ se
 #pragma unroll 2
     for (int t = 0; t < tc; ++t) {
       const float* tok = buf + (size_t)t * R;
-      float du0 = 0.f, du1 = 0.f, du2 = 0.f, du3 = 0.f;
+      float du[CPT][2];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) du[cc][0] = du[cc][1] = 0.f;
 #pragma unroll
       for (int q = 0; q < RPT / 4; ++q) {
         const float4 u = *reinterpret_cast<const float4*>(tok + 2 * P + 4 * q);
-        du0 = fmaf(u.x, S[4 * q], du0);
-        du1 = fmaf(u.y, S[4 * q + 1], du1);
-        du2 = fmaf(u.z, S[4 * q + 2], du2);
-        du3 = fmaf(u.w, S[4 * q + 3], du3);
-      }
-      float du = (du0 + du1) + (du2 + du3);
 #pragma unroll
-      for (int o = L >> 1; o > 0; o >>= 1) du += __shfl_xor_sync(0xffffffffu, du, o);
-      const float v = vbuf[(size_t)t * R];
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (int cc = 0; cc < CPT; ++cc) {
+          du[cc][0] = fmaf(u.y, S[cc][4 * q + 1], fmaf(u.x, S[cc][4 * q], du[cc][0]));
+          du[cc][1] = fmaf(u.w, S[cc][4 * q + 3], fmaf(u.z, S[cc][4 * q + 2], du[cc][1]));
+        }
+      }
+      float dus[CPT];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) dus[cc] = du[cc][0] + du[cc][1];
+#pragma unroll
+      for (int o = L >> 1; o > 0; o >>= 1)
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) dus[cc] += __shfl_xor_sync(0xffffffffu, dus[cc], o);
+      float v[CPT], acc[CPT][2];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) {
+        v[cc] = vbuf[(size_t)t * R + cc];
+        acc[cc][0] = acc[cc][1] = 0.f;
+      }
 #pragma unroll
       for (int q = 0; q < RPT / 4; ++q) {
         const float4 d = *reinterpret_cast<const float4*>(tok + 4 * q);
         const float4 au = *reinterpret_cast<const float4*>(tok + P + 4 * q);
         const float4 k = *reinterpret_cast<const float4*>(tok + 3 * P + 4 * q);
         const float4 r = *reinterpret_cast<const float4*>(tok + 4 * P + 4 * q);
-        S[4 * q] = fmaf(k.x, v, fmaf(-au.x, du, d.x * S[4 * q]));
-        S[4 * q + 1] = fmaf(k.y, v, fmaf(-au.y, du, d.y * S[4 * q + 1]));
-        S[4 * q + 2] = fmaf(k.z, v, fmaf(-au.z, du, d.z * S[4 * q + 2]));
-        S[4 * q + 3] = fmaf(k.w, v, fmaf(-au.w, du, d.w * S[4 * q + 3]));
-        a0 = fmaf(r.x, S[4 * q], a0);
-        a1 = fmaf(r.y, S[4 * q + 1], a1);
-        a2 = fmaf(r.z, S[4 * q + 2], a2);
-        a3 = fmaf(r.w, S[4 * q + 3], a3);
-      }
-      float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
-      for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (writer) op[(size_t)t * ostep] = acc;
+        for (int cc = 0; cc < CPT; ++cc) {
+          float* Sc = S[cc];
+          Sc[4 * q] = fmaf(k.x, v[cc], fmaf(-au.x, dus[cc], d.x * Sc[4 * q]));
+          Sc[4 * q + 1] = fmaf(k.y, v[cc], fmaf(-au.y, dus[cc], d.y * Sc[4 * q + 1]));
+          Sc[4 * q + 2] = fmaf(k.z, v[cc], fmaf(-au.z, dus[cc], d.z * Sc[4 * q + 2]));
+          Sc[4 * q + 3] = fmaf(k.w, v[cc], fmaf(-au.w, dus[cc], d.w * Sc[4 * q + 3]));
+          acc[cc][0] = fmaf(r.y, Sc[4 * q + 1], fmaf(r.x, Sc[4 * q], acc[cc][0]));
+          acc[cc][1] = fmaf(r.w, Sc[4 * q + 3], fmaf(r.z, Sc[4 * q + 2], acc[cc][1]));
+        }
+      }
+      float o_[CPT];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) o_[cc] = acc[cc][0] + acc[cc][1];
+#pragma unroll
+      for (int o = L >> 1; o > 0; o >>= 1)
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) o_[cc] += __shfl_xor_sync(0xffffffffu, o_[cc], o);
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc)
+        if (lead && col_ok[cc]) op[(size_t)t * ostep + cc] = o_[cc];
     }
     op += (size_t)tc * ostep;
     __syncthreads();                            // the stage may be filled again
   }
 #pragma unroll
-  for (int m = 0; m < RPT; ++m) {
-    const int i = sub + L * m;
-    if (col_ok && i < dk) sp[(size_t)i * dv + col] = S[m];
-  }
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int m = 0; m < RPT; ++m) {
+      const int i = sub + L * m;
+      if (col_ok[c] && i < dk) sp[(size_t)i * dv + col[c]] = S[c][m];
+    }
 }
 
 // The plain form of the scan for value sizes that are no multiple of 4 (records that are not whole 16-byte pieces):
@@ -241,15 +268,16 @@ HK_API int hk_delta_rule_record(int dk, int dv) {
   return most;
 }
 
-template <int RPT>
+template <int RPT, int CPT>
 static int dr_launch(int L, dim3 grid, int threads, size_t smem, cudaStream_t s, const float* rec, const int* segs, float* state,
                      float* out, int H, int dk, int dv, int cols, int chunk) {
 #define DR_LAUNCH(LL)                                                                                                       \
   do {                                                                                                                      \
     static HkSmemCache cache;                                                                                               \
-    int e = hk_allow_smem(delta_rule_scan_kernel<RPT, LL>, smem, cache);                                                    \
+    int e = hk_allow_smem(delta_rule_scan_kernel<RPT, LL, CPT>, smem, cache);                                               \
     if (e) return e;                                                                                                        \
-    return hk_launch(delta_rule_scan_kernel<RPT, LL>, grid, dim3(threads), smem, s, rec, segs, state, out, H, dk, dv, cols, chunk); \
+    return hk_launch(delta_rule_scan_kernel<RPT, LL, CPT>, grid, dim3(threads), smem, s, rec, segs, state, out, H, dk, dv, cols, \
+                     chunk);                                                                                                \
   } while (0)
   switch (L) {
     case 1: DR_LAUNCH(1);
@@ -299,15 +327,22 @@ HK_API int hk_delta_rule_scan(const float* r, const float* k, const float* v, co
   // block (256 blocks of 64 threads) against 1,096 with 32 and 839 with 4; below 4 every block fetches too much
   int cols = max(1, min(dv, 256 / L));
   while (cols > 8 && cols * L > 64 && (long long)n_seg * H * ((dv + cols - 1) / cols) < 2 * 148) cols >>= 1;
-  const int threads = ((cols * L + 31) / 32) * 32;
+  // two columns a lane group where a lane holds 8 state entries a column (they share the loads of the token's vectors,
+  // and their two chains of arithmetic hide each other's latency) and the block's columns are even
+  // (one request of 2,048 tokens: 64 heads of 64, 512 blocks: 1.00 ms against 1.12; 32 heads, 256 blocks: 0.89 against 0.78,
+  // so only where the blocks fill the SMs twice)
+  const bool many = (long long)n_seg * H * ((dv + cols - 1) / cols) >= 2 * 148;
+  const int cpt = (rpt == 8 && many && (cols & 1) == 0 && (dv & 1) == 0) ? 2 : 1;
+  const int threads = ((cols / cpt * L + 31) / 32) * 32;
   int chunk = 16;
   while (chunk > 2 && (size_t)2 * chunk * R * sizeof(float) > 64 * 1024) chunk >>= 1;
   const size_t smem = (size_t)2 * chunk * R * sizeof(float);
   dim3 grid((unsigned)(n_seg * H), (unsigned)((dv + cols - 1) / cols));
-  if (rpt == 8) return dr_launch<8>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
-  if (rpt == 16) return dr_launch<16>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
-  if (rpt == 32) return dr_launch<32>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
-  return dr_launch<64>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
+  if (rpt == 8 && cpt == 2) return dr_launch<8, 2>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
+  if (rpt == 8) return dr_launch<8, 1>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
+  if (rpt == 16) return dr_launch<16, 1>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
+  if (rpt == 32) return dr_launch<32, 1>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
+  return dr_launch<64, 1>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
 }
 
 // ------------------------------------------------------------------ generalised delta rule: the output's gate
