@@ -321,7 +321,6 @@ grouped_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, TO* __rest
 #define GM_BN 128
 #define GM_BK 32
 #define GM_LD (GM_BK + 8)
-#define GM_STAGES 3
 
 __device__ __forceinline__ uint32_t gm_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void gm_cp_async16(void* dst, const void* src, bool valid) {
@@ -339,12 +338,16 @@ __device__ __forceinline__ void gm_mma(float* c, const uint32_t* a, uint32_t b0,
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool GATED>
+// GM_STAGES: slices in the ring (dynamic shared memory): all but one on their way while one is multiplied.
+template <bool GATED, int GM_STAGES>
 __global__ void __launch_bounds__(256)
 grouped_gemm_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, void* __restrict__ out_, const int* __restrict__ tiles,
                         const int* __restrict__ offsets, const int* __restrict__ perm, int top, int gather, int N, int K) {
-  __shared__ __align__(16) bf16 As[GM_STAGES][RT_BM][GM_LD];
-  __shared__ __align__(16) bf16 Ws[GM_STAGES][GM_BN][GM_LD];
+  extern __shared__ __align__(16) uint8_t gm_smem[];
+  typedef bf16 (*ATile)[RT_BM][GM_LD];
+  typedef bf16 (*WTile)[GM_BN][GM_LD];
+  ATile As = reinterpret_cast<ATile>(gm_smem);                                               // [GM_STAGES][RT_BM][GM_LD]
+  WTile Ws = reinterpret_cast<WTile>(gm_smem + sizeof(bf16) * GM_STAGES * RT_BM * GM_LD);    // [GM_STAGES][GM_BN][GM_LD]
   __shared__ int rows[RT_BM];
   const int e = tiles[2 * blockIdx.y];
   if (e < 0) return;
@@ -392,12 +395,15 @@ grouped_gemm_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
   const int ksteps = (K + GM_BK - 1) / GM_BK;
-  load(0, 0);
-  if (ksteps > 1) load(1, GM_BK); else asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+  for (int pre = 0; pre < GM_STAGES - 1; ++pre) {      // one group per slice, also past the end: the counting below relies on it
+    if (pre < ksteps) load(pre, pre * GM_BK); else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   for (int ks = 0; ks < ksteps; ++ks) {
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(GM_STAGES - 2) : "memory");
     __syncthreads();                                  // stage ks has landed; stage ks - 1 is free for everyone
-    if (ks + 2 < ksteps) load((ks + 2) % GM_STAGES, (ks + 2) * GM_BK); else asm volatile("cp.async.commit_group;" ::: "memory");
+    if (ks + GM_STAGES - 1 < ksteps) load((ks + GM_STAGES - 1) % GM_STAGES, (ks + GM_STAGES - 1) * GM_BK);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
     const int st = ks % GM_STAGES;
 #pragma unroll
     for (int kk = 0; kk < GM_BK; kk += 16) {
@@ -445,6 +451,17 @@ grouped_gemm_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
     }
 }
 
+template <bool GATED, int STAGES>
+static int gm_launch(const void* a, const void* w, void* out, const int* tiles, int max_tiles, const int* offsets, const int* perm,
+                     int top, int gather, int N, int K, cudaStream_t s) {
+  const size_t smem = sizeof(bf16) * STAGES * (RT_BM + GM_BN) * GM_LD;
+  static HkSmemCache cache;
+  if (int e = hk_allow_smem(grouped_gemm_mma_kernel<GATED, STAGES>, smem, cache)) return e;
+  dim3 grid((unsigned)((N + (GATED ? 63 : GM_BN - 1)) / (GATED ? 64 : GM_BN)), (unsigned)max_tiles);
+  return hk_launch(grouped_gemm_mma_kernel<GATED, STAGES>, grid, dim3(256), smem, s, (const bf16*)a, (const bf16*)w, out, tiles, offsets,
+                   perm, top, gather, N, K);
+}
+
 HK_API int hk_grouped_gemm(const void* a, const void* w, int dtype, void* out, const int* tiles, int max_tiles, const int* offsets,
                            const int* perm, int top, int gather, int N, int K, int gated, void* stream) {
   if (max_tiles <= 0 || N <= 0) return 0;
@@ -459,14 +476,14 @@ HK_API int hk_grouped_gemm(const void* a, const void* w, int dtype, void* out, c
                      tiles, offsets, perm, top, gather, N, K);
   }
   if (dtype == HK_BF16 && (K & 7) == 0 && ((((uintptr_t)a | (uintptr_t)w) & 15) == 0)) {
-    if (gated) {
-      dim3 g2((unsigned)((N + 63) / 64), (unsigned)max_tiles);
-      return hk_launch(grouped_gemm_mma_kernel<true>, g2, dim3(256), 0, s, (const bf16*)a, (const bf16*)w, out, tiles, offsets, perm,
-                       top, gather, N, K);
-    }
-    dim3 g2((unsigned)((N + GM_BN - 1) / GM_BN), (unsigned)max_tiles);
-    return hk_launch(grouped_gemm_mma_kernel<false>, g2, dim3(256), 0, s, (const bf16*)a, (const bf16*)w, out, tiles, offsets, perm,
-                     top, gather, N, K);
+    // few rows (decode steps): the products are bound by the experts' weight bytes, and a ring of six slices keeps more of
+    // them on their way (width 4,096, 128 pairs: 88 and 45 us against 97 and 57 with three); many rows: three slices leave
+    // room for four CTAs an SM (4,096 pairs: 546 and 297 us against 653 and 307 with six)
+    const bool deep = max_tiles <= 40;       // tiles = pairs / 64 + experts: a few hundred pairs at most
+    if (gated) return deep ? gm_launch<true, 6>(a, w, out, tiles, max_tiles, offsets, perm, top, gather, N, K, s)
+                           : gm_launch<true, 3>(a, w, out, tiles, max_tiles, offsets, perm, top, gather, N, K, s);
+    return deep ? gm_launch<false, 6>(a, w, out, tiles, max_tiles, offsets, perm, top, gather, N, K, s)
+                : gm_launch<false, 3>(a, w, out, tiles, max_tiles, offsets, perm, top, gather, N, K, s);
   }
   if (dtype == HK_BF16) {
     if (gated)
