@@ -7,9 +7,17 @@
 // the keys round-robin, each keeping an online softmax state (max, sum, weighted values); the
 // four states are merged in a fixed order.  Nothing depends on which other tokens are in the
 // batch, so the result at a position is the same under every way of cutting the work.
-// Values may be narrower than keys (`vd` <= hd: pages [page][G][page_tokens][vd], out [n, H * vd]).  With
+// Values may have another width than keys (`vd`: pages [page][G][page_tokens][vd], out [n, H * vd]).  With
 // `sink` = 1 the softmax has one more term in its denominator, a key whose score is 0 and that has no value:
-// p_j = exp(s_j) / (1 + sum exp(s_j)).
+// p_j = exp(s_j) / (1 + sum exp(s_j)); with `sinks` (one float per query head) that key's score is sinks[h] instead of 0.
+// Further options, each off at 0 or null:
+//   softcap c   a score becomes c * tanh(score / c) before the softmax;
+//   chunk s     a token also sees no key before the start of its own block of s positions, (p / s) * s, counted from
+//               position 0 of the request;
+//   v_stride    elements between the values of consecutive tokens of a page; when it is not vd the values lie inside
+//               wider rows: a cache that keeps ONE tensor per token whose first vd dims are the value (v_pages = k_pages,
+//               v_stride = hd);
+//   gate        fp32 logits [n, gate_ld >= H * vd]: the output is multiplied by sigmoid(gate[t, h * vd + d]).
 //
 // Reference counterpart: `attention`, src/cuda_device.zig:1494-1594 (block per (token, head),
 // warp per position, online softmax); scale on q first: src/engine/attention_kernel.zig:109.
@@ -18,15 +26,24 @@
 #include "common.cuh"
 
 #define AG_WARPS 4
-#define AG_MAX_PER_LANE 8  // head_dim <= 256
 
-template <typename T>
+struct AgOptions {
+  float softcap;
+  int chunk;
+  int v_stride;
+  const float* sinks;
+  const float* gate;
+  long long gate_ld;
+};
+
+// AG_MAX_PER_LANE: dims per lane, 8 for widths up to 256, 20 up to 640
+template <typename T, int AG_MAX_PER_LANE>
 __global__ void __launch_bounds__(AG_WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                          const T* __restrict__ v_pages, const int* __restrict__ block_table,
                          int table_stride, const int* __restrict__ positions,
                          const int* __restrict__ slot_of_token, T* __restrict__ out, int H, int G, int hd,
-                         int page_tokens, int window, float scale, int vd, int sink) {
+                         int page_tokens, int window, float scale, int vd, int sink, AgOptions opt) {
   extern __shared__ float smem[];  // [AG_WARPS][vd] values, then [AG_WARPS] max, [AG_WARPS] sum
   float* acc_s = smem;
   float* m_s = smem + AG_WARPS * vd;
@@ -38,6 +55,8 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
   int pos = positions[t];
   const int* bt = block_table + (size_t)slot_of_token[t] * table_stride;
   int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  if (opt.chunk > 0) lo = max(lo, (pos / opt.chunk) * opt.chunk);
+  const float cap = opt.softcap, inv_cap = opt.softcap > 0.f ? 1.0f / opt.softcap : 0.f;
 
   float qr[AG_MAX_PER_LANE], acc[AG_MAX_PER_LANE];
   const T* qp = q + ((size_t)t * H + h) * hd;
@@ -53,7 +72,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     if (page < 0) continue;  // never scheduled by the host; keeps the reads in bounds
     const size_t at = ((size_t)page * G + g) * page_tokens + (j % page_tokens);
     const T* kp = k_pages + at * hd;
-    const T* vp = v_pages + at * vd;
+    const T* vp = v_pages + at * opt.v_stride;
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < AG_MAX_PER_LANE; ++i) {
@@ -61,6 +80,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
       if (d < hd) s = fmaf(qr[i], to_f32<T>(kp[d]), s);
     }
     s = warp_sum(s);
+    if (cap > 0.f) s = cap * tanhf(s * inv_cap);
     float mn = fmaxf(m, s);
     float corr = expf(m - mn);
     float p = expf(s - mn);
@@ -82,7 +102,8 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     l_s[wid] = l;
   }
   __syncthreads();
-  float mm = sink ? 0.f : m_s[0];   // the sink's score takes part in the maximum
+  const float sink_score = sink && opt.sinks ? opt.sinks[h] : 0.f;
+  float mm = sink ? sink_score : m_s[0];   // the sink's score takes part in the maximum
 #pragma unroll
   for (int w = sink ? 0 : 1; w < AG_WARPS; ++w) mm = fmaxf(mm, m_s[w]);
   float f[AG_WARPS], lt = 0.f;
@@ -91,34 +112,44 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     f[w] = m_s[w] == -CUDART_INF_F ? 0.f : expf(m_s[w] - mm);
     lt += l_s[w] * f[w];
   }
-  if (sink) lt += expf(-mm);
+  if (sink) lt += expf(sink_score - mm);
   T* op = out + ((size_t)t * H + h) * vd;
   for (int d = threadIdx.x; d < vd; d += blockDim.x) {
     float a = 0.f;
 #pragma unroll
     for (int w = 0; w < AG_WARPS; ++w) a += acc_s[w * vd + d] * f[w];
-    op[d] = from_f32<T>(a / lt);
+    a /= lt;
+    if (opt.gate) a /= 1.0f + expf(-opt.gate[(size_t)t * opt.gate_ld + (size_t)h * vd + d]);
+    op[d] = from_f32<T>(a);
   }
+}
+
+template <typename T, int PER>
+static int ag_launch(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
+                     const int* positions, const int* slot_of_token, void* out, int n, int H, int G, int hd, int page_tokens,
+                     int window, float scale, int vd, int sink, AgOptions opt, cudaStream_t s) {
+  size_t smem = (size_t)(AG_WARPS * vd + 2 * AG_WARPS) * sizeof(float);
+  unsigned blocks = (unsigned)((long long)n * H);
+  attention_generic_kernel<T, PER><<<blocks, AG_WARPS * 32, smem, s>>>(
+      (const T*)q, (const T*)k_pages, (const T*)v_pages, block_table, table_stride, positions, slot_of_token, (T*)out, H, G, hd,
+      page_tokens, window, scale, vd, sink, opt);
+  return hk_launch_status();
 }
 
 HK_API int hk_attention_generic(const void* q, const void* k_pages, const void* v_pages, int dtype,
                                 const int* block_table, int table_stride, const int* positions,
                                 const int* slot_of_token, void* out, int n, int H, int G, int hd,
-                                int page_tokens, int window, float scale, int vd, int sink, void* stream) {
+                                int page_tokens, int window, float scale, int vd, int sink, const float* sinks, float softcap,
+                                int chunk, int v_stride, const float* gate, long long gate_ld, void* stream) {
   if (n <= 0) return 0;
-  if (hd > 32 * AG_MAX_PER_LANE || hd < 1 || G < 1 || H % G != 0 || vd < 1 || vd > hd) return HK_ERR_UNSUPPORTED;
+  const int widest = hd > vd ? hd : vd;
+  if (widest > 640 || hd < 1 || G < 1 || H % G != 0 || vd < 1 || v_stride < vd || softcap < 0.f || chunk < 0) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-  size_t smem = (size_t)(AG_WARPS * vd + 2 * AG_WARPS) * sizeof(float);
-  unsigned blocks = (unsigned)((long long)n * H);
-  if (dtype == HK_F32)
-    attention_generic_kernel<float><<<blocks, AG_WARPS * 32, smem, s>>>(
-        (const float*)q, (const float*)k_pages, (const float*)v_pages, block_table, table_stride, positions,
-        slot_of_token, (float*)out, H, G, hd, page_tokens, window, scale, vd, sink);
-  else if (dtype == HK_BF16)
-    attention_generic_kernel<bf16><<<blocks, AG_WARPS * 32, smem, s>>>(
-        (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, positions,
-        slot_of_token, (bf16*)out, H, G, hd, page_tokens, window, scale, vd, sink);
-  else
-    return HK_ERR_UNSUPPORTED;
-  return hk_launch_status();
+  AgOptions opt = {softcap, chunk, v_stride, sinks, gate, gate_ld};
+  if (dtype != HK_F32 && dtype != HK_BF16) return HK_ERR_UNSUPPORTED;
+#define AG_GO(T, PER) ag_launch<T, PER>(q, k_pages, v_pages, block_table, table_stride, positions, slot_of_token, out, n, H, G, hd, \
+                                        page_tokens, window, scale, vd, sink, opt, s)
+  if (widest <= 256) return dtype == HK_F32 ? AG_GO(float, 8) : AG_GO(bf16, 8);
+  return dtype == HK_F32 ? AG_GO(float, 20) : AG_GO(bf16, 20);
+#undef AG_GO
 }

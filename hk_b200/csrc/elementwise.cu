@@ -10,22 +10,28 @@
 #include "common.cuh"
 
 // ----------------------------------------------------------------------------- embedding
-// out[t, :] = table[ids[t], :] widened to fp32 (the residual stream is fp32).
+// out[t, :] = table[ids[t], :] widened to fp32 (the residual stream is fp32) and multiplied by `scale` (1 for
+// none).  `narrow` (or null) receives the same row rounded to bf16: the input of a first sublayer that reads the
+// residual stream itself.
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int n, int d, int vocab) {
+                                 float* __restrict__ out, int n, int d, int vocab, float scale, bf16* __restrict__ narrow) {
   int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;  // the host validates ids; this only keeps the read in bounds
   const T* src = table + (size_t)id * d;
   float* dst = out + (size_t)t * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = to_f32<T>(src[i]) * scale;
+    dst[i] = v;
+    if (narrow) narrow[(size_t)t * d + i] = __float2bfloat16_rn(v);
+  }
 }
 
 // The same with 16-byte loads (8 bf16 or 4 floats per thread and step), all issued before any is used.
 template <typename T, int PER>
 __global__ void embedding_vec_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                                     int d, int vocab) {
+                                     int d, int vocab, float scale, bf16* __restrict__ narrow) {
   constexpr int E = 16 / sizeof(T);   // elements per 16-byte load
   pdl_launch_dependents();
   pdl_wait();
@@ -48,23 +54,29 @@ __global__ void embedding_vec_kernel(const T* __restrict__ table, const int* __r
     const T* e = reinterpret_cast<const T*>(&v[k]);
     float f[E];
 #pragma unroll
-    for (int i = 0; i < E; ++i) f[i] = to_f32<T>(e[i]);
+    for (int i = 0; i < E; ++i) f[i] = to_f32<T>(e[i]) * scale;
 #pragma unroll
     for (int i = 0; i < E; i += 4) *reinterpret_cast<float4*>(dst + c * E + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+    if (narrow) {
+#pragma unroll
+      for (int i = 0; i < E; i += 2)
+        *reinterpret_cast<__nv_bfloat162*>(narrow + (size_t)t * d + c * E + i) = __floats2bfloat162_rn(f[i], f[i + 1]);
+    }
   }
 }
 
 HK_API int hk_embedding(const void* table, int table_dtype, const int* ids, float* out, int n, int d,
-                        int vocab, void* stream) {
+                        int vocab, float scale, void* narrow_out, void* stream) {
+  bf16* narrow = (bf16*)narrow_out;
   if (n <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   {
     const int e = table_dtype == HK_F32 ? 4 : 8;
     if (d % e == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0 && d / e <= 4 * 256) {
       if (table_dtype == HK_F32)
-        return hk_launch(embedding_vec_kernel<float, 4>, dim3(n), dim3(256), 0, s, (const float*)table, ids, out, d, vocab);
+        return hk_launch(embedding_vec_kernel<float, 4>, dim3(n), dim3(256), 0, s, (const float*)table, ids, out, d, vocab, scale, narrow);
       else if (table_dtype == HK_BF16)
-        return hk_launch(embedding_vec_kernel<bf16, 4>, dim3(n), dim3(256), 0, s, (const bf16*)table, ids, out, d, vocab);
+        return hk_launch(embedding_vec_kernel<bf16, 4>, dim3(n), dim3(256), 0, s, (const bf16*)table, ids, out, d, vocab, scale, narrow);
       else
         return HK_ERR_UNSUPPORTED;
       return hk_launch_status();
@@ -72,9 +84,9 @@ HK_API int hk_embedding(const void* table, int table_dtype, const int* ids, floa
   }
   int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == HK_F32)
-    embedding_kernel<float><<<n, threads, 0, s>>>((const float*)table, ids, out, n, d, vocab);
+    embedding_kernel<float><<<n, threads, 0, s>>>((const float*)table, ids, out, n, d, vocab, scale, narrow);
   else if (table_dtype == HK_BF16)
-    embedding_kernel<bf16><<<n, threads, 0, s>>>((const bf16*)table, ids, out, n, d, vocab);
+    embedding_kernel<bf16><<<n, threads, 0, s>>>((const bf16*)table, ids, out, n, d, vocab, scale, narrow);
   else
     return HK_ERR_UNSUPPORTED;
   return hk_launch_status();
@@ -204,7 +216,8 @@ HK_API int hk_rms_norm(const float* x, const float* w, const int* rows, void* ou
 }
 
 // ------------------------------------------------- per-head norm + rotation + cache write
-// One warp per (token, head) of the fused projection output qkv[n, (H + 2G) * hd] (fp32):
+// One warp per (token, head) of the fused projection output qkv[n, (H + G) * hd + G * vd] (fp32; the value heads may
+// have a width vd of their own):
 //   q heads: optional RMS norm over hd (weight shared by the heads), rotate-half rotation of
 //            the first `rot` dims by the token's position, stored to q_out[n, H*hd];
 //   k heads: the same with the key norm weight, stored into the token's cache page;
@@ -227,7 +240,7 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
     const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
-    int write_kv, const float* __restrict__ bias, int pairing, int norm_after, int tied_v, int vd) {
+    int write_kv, const float* __restrict__ bias, int pairing, int norm_after, int tied_v, int vd, long long ld) {
   __shared__ float buf[QKR_WARPS][QKR_MAX_HD];
   pdl_launch_dependents();
   pdl_wait();
@@ -238,17 +251,21 @@ __global__ void qk_norm_rope_kv_write_kernel(
   if (item >= (long long)n * heads_total) return;
   int t = (int)(item / heads_total);
   int hh = (int)(item % heads_total);
-  const float* src = qkv + (size_t)t * (H + kv_heads) * hd + (size_t)hh * hd;
+  int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);  // q, k, v
+  // a row holds H + G heads of hd, then (unless the values are the keys) G value heads of vd
+  const size_t row = (size_t)ld;   // at least (H + G) * hd + (tied_v ? 0 : G * vd): further columns are not read
+  const size_t col = kind == 2 ? (size_t)(H + G) * hd + (size_t)(hh - H - G) * vd : (size_t)hh * hd;
+  const int width_in = kind == 2 ? vd : hd;
+  const float* src = qkv + (size_t)t * row + col;
   float* v = buf[wid];
   float ss = 0.f;
-  for (int i = lane; i < hd; i += 32) {
+  for (int i = lane; i < width_in; i += 32) {
     float a = src[i];
-    if (bias) a += bias[(size_t)hh * hd + i];
+    if (bias) a += bias[col + i];
     v[i] = a;
     ss = fmaf(a, a, ss);
   }
   __syncwarp();
-  int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);  // q, k, v
   int pos = positions[t];
   int page = -1;
   if (kind != 0) {
@@ -314,7 +331,7 @@ qk_norm_rope_kv_write_vec_kernel(
     const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
     const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
-    int write_kv, const float* __restrict__ bias, int pairing, int norm_after, int tied_v, int vd) {
+    int write_kv, const float* __restrict__ bias, int pairing, int norm_after, int tied_v, int vd, long long ld) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -325,14 +342,16 @@ qk_norm_rope_kv_write_vec_kernel(
   const int t = (int)(item / heads_total);
   const int hh = (int)(item % heads_total);
   const int d0 = lane * 4;
-  const bool active = d0 < hd;
-  const float* src = qkv + (size_t)t * (H + kv_heads) * hd + (size_t)hh * hd;
+  const int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);
+  const size_t row = (size_t)ld;   // at least (H + G) * hd + (tied_v ? 0 : G * vd): further columns are not read
+  const size_t col = kind == 2 ? (size_t)(H + G) * hd + (size_t)(hh - H - G) * vd : (size_t)hh * hd;
+  const bool active = d0 < (kind == 2 ? vd : hd);
+  const float* src = qkv + (size_t)t * row + col;
   float4 v = active ? *reinterpret_cast<const float4*>(src + d0) : make_float4(0.f, 0.f, 0.f, 0.f);
   if (bias && active) {
-    const float4 b = *reinterpret_cast<const float4*>(bias + (size_t)hh * hd + d0);
+    const float4 b = *reinterpret_cast<const float4*>(bias + col + d0);
     v = make_float4(v.x + b.x, v.y + b.y, v.z + b.z, v.w + b.w);
   }
-  const int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);
   const int pos = positions[t];
   int page = 0;
   if (kind != 0) page = block_table[(size_t)slot_of_token[t] * table_stride + pos / page_tokens];
@@ -403,7 +422,6 @@ qk_norm_rope_kv_write_vec_kernel(
   } else if (kind == 1) {
     dst = k_pages + (((size_t)page * G + (hh - H)) * page_tokens + (pos % page_tokens)) * hd;
   } else {
-    if (d0 >= vd) return;
     dst = v_pages + (((size_t)page * G + (hh - H - G)) * page_tokens + (pos % page_tokens)) * vd;
   }
   if (sizeof(T) == 4) {
@@ -421,35 +439,36 @@ HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, co
                                     const int* block_table, int table_stride, void* k_pages,
                                     void* v_pages, int n, int H, int G, int hd, int page_tokens,
                                     int write_kv, const float* bias, int pairing, int norm_after, int tied_v, int vd,
-                                    void* stream) {
+                                    long long ld, void* stream) {
+  if (ld <= 0) ld = (long long)(H + G) * hd + (tied_v ? 0 : (long long)G * vd);
   if (n <= 0) return 0;
   if (hd > QKR_MAX_HD || hd < 2 || rot > hd || (rot & 1) || pairing < 0 || pairing > 1) return HK_ERR_UNSUPPORTED;
-  if (vd < 1 || vd > hd) return HK_ERR_UNSUPPORTED;
+  if (vd < 1 || vd > QKR_MAX_HD || (tied_v && vd > hd)) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   long long items = (long long)n * (H + (write_kv ? (tied_v ? G : 2 * G) : 0));
   const bool aligned = ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)q_w |
                           (uintptr_t)k_w | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)bias) & 15) == 0);
-  if (hd <= 128 && (hd & 3) == 0 && (vd & 3) == 0 && (rot & 7) == 0 && aligned) {
+  if (hd <= 128 && vd <= 128 && (hd & 3) == 0 && (vd & 3) == 0 && (rot & 7) == 0 && (ld & 3) == 0 && aligned) {
     unsigned vblocks = (unsigned)((items + QKV_WARPS - 1) / QKV_WARPS);
     if (dtype == HK_F32)
       return hk_launch_pdl(qk_norm_rope_kv_write_vec_kernel<float>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (float*)q_out,
                        q_w, k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (float*)k_pages,
-                       (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd);
+                       (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd, ld);
     if (dtype == HK_BF16)
       return hk_launch_pdl(qk_norm_rope_kv_write_vec_kernel<bf16>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
                        k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (bf16*)k_pages,
-                       (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd);
+                       (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd, ld);
     return HK_ERR_UNSUPPORTED;
   }
   unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
   if (dtype == HK_F32)
     return hk_launch(qk_norm_rope_kv_write_kernel<float>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, qkv, (float*)q_out, q_w,
                          k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (float*)k_pages,
-                         (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd);
+                         (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd, ld);
   if (dtype == HK_BF16)
     return hk_launch(qk_norm_rope_kv_write_kernel<bf16>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
                          k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (bf16*)k_pages,
-                         (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd);
+                         (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing, norm_after, tied_v, vd, ld);
   return HK_ERR_UNSUPPORTED;
 }
 
@@ -469,8 +488,14 @@ HK_API int hk_add_bias(float* out, const float* bias, int n, int N, void* stream
 // ----------------------------------------------------------------------------- swiglu
 // out[t, j] = silu(gate_j) * up_j for the fused projection gu[n, 2F], laid out in blocks of
 // `block` gates followed by the matching `block` ups (block == F: all gates, then all ups).
+// `act` chooses the gate's activation: 0 = silu (SwiGLU), 1 = the tanh form of gelu (GeGLU).
+__device__ __forceinline__ float glu_act(float g, int act) {
+  if (act == 0) return g / (1.0f + expf(-g));
+  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
 template <typename TO>
-__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F, int block) {
+__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F, int block, int act) {
   pdl_launch_dependents();
   pdl_wait();
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -480,26 +505,27 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out
   long long gi = t * 2 * F + (long long)(j / block) * 2 * block + (j % block);
   float g = gu[gi];
   float u = gu[gi + block];
-  out[i] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
+  out[i] = from_f32<TO>(glu_act(g, act) * u);
 }
 
-HK_API int hk_swiglu(const float* gu, void* out, int out_dtype, int n, int F, int block, void* stream) {
+HK_API int hk_swiglu(const float* gu, void* out, int out_dtype, int n, int F, int block, int act, void* stream) {
   if (n <= 0) return 0;
-  if (block <= 0 || F % block) return HK_ERR_UNSUPPORTED;
+  if (block <= 0 || F % block || act < 0 || act > 1) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   long long total = (long long)n * F;
   unsigned blocks = (unsigned)((total + 255) / 256);
-  if (out_dtype == HK_F32) return hk_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, s, gu, (float*)out, total, F, block);
-  if (out_dtype == HK_BF16) return hk_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, gu, (bf16*)out, total, F, block);
+  if (out_dtype == HK_F32) return hk_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, s, gu, (float*)out, total, F, block, act);
+  if (out_dtype == HK_BF16) return hk_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, gu, (bf16*)out, total, F, block, act);
   return HK_ERR_UNSUPPORTED;
 }
 
 // ----------------------------------------------------------------------------- norm of a sublayer's output, added
 // residual[r, :] += y[r, :] * rsqrt(mean(y^2) + eps) * w: the norm AFTER a mixer or feed-forward of a layer that
 // norms both sides of its sublayers, fused with the residual sum (which stays fp32).  Same summation order as
-// `rms_norm_kernel`.
+// `rms_norm_kernel`.  `narrow` (or null) receives the new residual row rounded to bf16: the input of a next sublayer
+// that reads the residual stream itself (a layer that norms only behind its sublayers).
 __global__ void rms_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ residual,
-                                    int d, float eps) {
+                                    int d, float eps, bf16* __restrict__ narrow) {
   __shared__ float warp_part[32];
   __shared__ float inv_s;
   const int r = blockIdx.x;
@@ -521,14 +547,19 @@ __global__ void rms_norm_add_kernel(const float* __restrict__ y, const float* __
   __syncthreads();
   const float inv = inv_s;
   float* dst = residual + (size_t)r * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] += src[i] * inv * w[i];
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = dst[i] + src[i] * inv * w[i];
+    dst[i] = v;
+    if (narrow) narrow[(size_t)r * d + i] = __float2bfloat16_rn(v);
+  }
 }
 
 // The same for widths that are a multiple of 4 and at most 4 * PER * 256: the row is read once with 16-byte loads that
 // are all in flight together and stays in registers between the two passes (as `rms_norm_vec_kernel`).
 template <int PER>
 __global__ void __launch_bounds__(256)
-rms_norm_add_vec_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ residual, int d, float eps) {
+rms_norm_add_vec_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ residual, int d, float eps,
+                        bf16* __restrict__ narrow) {
   __shared__ float warp_part[8];
   __shared__ float inv_s;
   const int r = blockIdx.x;
@@ -568,24 +599,33 @@ rms_norm_add_vec_kernel(const float* __restrict__ y, const float* __restrict__ w
 #pragma unroll
   for (int k = 0; k < PER; ++k) {
     const int c = threadIdx.x + k * 256;
-    if (c < chunks)
-      dst[c] = make_float4(x[k].x + v[k].x * inv * g[k].x, x[k].y + v[k].y * inv * g[k].y, x[k].z + v[k].z * inv * g[k].z,
-                           x[k].w + v[k].w * inv * g[k].w);
+    if (c < chunks) {
+      const float4 o = make_float4(x[k].x + v[k].x * inv * g[k].x, x[k].y + v[k].y * inv * g[k].y, x[k].z + v[k].z * inv * g[k].z,
+                                   x[k].w + v[k].w * inv * g[k].w);
+      dst[c] = o;
+      if (narrow) {
+        __nv_bfloat162 lo2 = __floats2bfloat162_rn(o.x, o.y), hi2 = __floats2bfloat162_rn(o.z, o.w);
+        *reinterpret_cast<uint2*>(narrow + (size_t)r * d + 4 * c) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&lo2), *reinterpret_cast<uint32_t*>(&hi2));
+      }
+    }
   }
 }
 
-HK_API int hk_rms_norm_add(const float* y, const float* w, float* residual, int n, int d, float eps, void* stream) {
+HK_API int hk_rms_norm_add(const float* y, const float* w, float* residual, int n, int d, float eps, void* narrow_out,
+                           void* stream) {
   if (n <= 0) return 0;
-  if ((d & 3) == 0 && d >= 512 && (((uintptr_t)y | (uintptr_t)w | (uintptr_t)residual) & 15) == 0) {
+  bf16* narrow = (bf16*)narrow_out;
+  if ((d & 3) == 0 && d >= 512 && (((uintptr_t)y | (uintptr_t)w | (uintptr_t)residual) & 15) == 0 && ((uintptr_t)narrow & 7) == 0) {
     const int chunks = d >> 2;
     cudaStream_t s = (cudaStream_t)stream;
-    if (chunks <= 256) return hk_launch(rms_norm_add_vec_kernel<1>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps);
-    if (chunks <= 2 * 256) return hk_launch(rms_norm_add_vec_kernel<2>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps);
-    if (chunks <= 4 * 256) return hk_launch(rms_norm_add_vec_kernel<4>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps);
-    if (chunks <= 8 * 256) return hk_launch(rms_norm_add_vec_kernel<8>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps);
+    if (chunks <= 256) return hk_launch(rms_norm_add_vec_kernel<1>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps, narrow);
+    if (chunks <= 2 * 256) return hk_launch(rms_norm_add_vec_kernel<2>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps, narrow);
+    if (chunks <= 4 * 256) return hk_launch(rms_norm_add_vec_kernel<4>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps, narrow);
+    if (chunks <= 8 * 256) return hk_launch(rms_norm_add_vec_kernel<8>, dim3((unsigned)n), dim3(256), 0, s, y, w, residual, d, eps, narrow);
   }
   return hk_launch(rms_norm_add_kernel, dim3((unsigned)n), dim3(d >= 2048 ? 256 : 128), 0, (cudaStream_t)stream, y, w, residual, d,
-                   eps);
+                   eps, narrow);
 }
 
 // ----------------------------------------------------------------------------- polynomial activation with norms
@@ -739,5 +779,114 @@ HK_API int hk_tanh_cols(const float* x, long long ld, void* out, int out_dtype, 
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (out_dtype == HK_F32) return hk_launch(tanh_cols_kernel<float>, dim3(blocks), dim3(256), 0, s, x, ld, (float*)out, total, R);
   if (out_dtype == HK_BF16) return hk_launch(tanh_cols_kernel<bf16>, dim3(blocks), dim3(256), 0, s, x, ld, (bf16*)out, total, R);
+  return HK_ERR_UNSUPPORTED;
+}
+
+// ----------------------------------------------------------------------------- output gate of a mixer
+// out[t, j] = x[t, j] * sigmoid(gate[t, j]) for x [n, W] (fp32, or the storage type) and the gate's logits as a column
+// slice of a fused projection's fp32 output (row stride ld).
+template <typename TI, typename TO>
+__global__ void sigmoid_gate_kernel(const TI* __restrict__ x, const float* __restrict__ gate, long long ld, TO* __restrict__ out,
+                                    long long total, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / W;
+  const int j = (int)(i % W);
+  const float g = gate[t * ld + j];
+  out[i] = from_f32<TO>(to_f32<TI>(x[i]) / (1.0f + expf(-g)));
+}
+
+HK_API int hk_sigmoid_gate(const void* x, int x_dtype, const float* gate, long long ld, void* out, int out_dtype, int n, int W,
+                           void* stream) {
+  if (n <= 0 || W <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long total = (long long)n * W;
+  const dim3 grid((unsigned)((total + 255) / 256)), block(256);
+  if (x_dtype == HK_F32 && out_dtype == HK_F32)
+    return hk_launch(sigmoid_gate_kernel<float, float>, grid, block, 0, s, (const float*)x, gate, ld, (float*)out, total, W);
+  if (x_dtype == HK_F32 && out_dtype == HK_BF16)
+    return hk_launch(sigmoid_gate_kernel<float, bf16>, grid, block, 0, s, (const float*)x, gate, ld, (bf16*)out, total, W);
+  if (x_dtype == HK_BF16 && out_dtype == HK_BF16)
+    return hk_launch(sigmoid_gate_kernel<bf16, bf16>, grid, block, 0, s, (const bf16*)x, gate, ld, (bf16*)out, total, W);
+  return HK_ERR_UNSUPPORTED;
+}
+
+// ----------------------------------------------------------------------------- latent attention: what a token brings
+// A mixer that caches one compressed vector per token instead of keys and values.  One warp per (token, item) of the fused
+// projection's fp32 output row [H query heads of (dn + dr) | r + dr compressed | ...] (row stride ld):
+//   query head h: its first dn dims go unchanged to q_plain[t, h, :dn] (they are multiplied with the keys' up-projection
+//                 afterwards); its last dr dims are rotated by the token's position into q_full[t, h, r : r + dr];
+//   the compressed row: its first r dims are RMS-normed with `c_w` (the latent), its last dr dims are rotated (the one
+//                 rotated key part that all heads share); both go to the token's cache row [page][1][page_tokens][r + dr].
+// The rotation turns the first `rot` of the dr dims, pairing 0: (i, i + rot/2), 1: (2i, 2i + 1); the tables carry any
+// magnitude factor.  With write_kv == 0 only the queries are produced.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ q_plain, T* __restrict__ q_full,
+                   const float* __restrict__ c_w, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                   int rot, int pairing, const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                   const int* __restrict__ block_table, int table_stride, T* __restrict__ pages, int n, int H, int dn, int dr,
+                   int r, int page_tokens, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int items = H + (write_kv ? 1 : 0);
+  const long long item = (long long)blockIdx.x * 4 + wid;
+  if (item >= (long long)n * items) return;
+  const int t = (int)(item / items), it = (int)(item % items);
+  const int pos = positions[t];
+  const float* row = proj + (size_t)t * ld;
+  const int half = rot >> 1;
+  const float* c = cos_t + (size_t)pos * half;
+  const float* s = sin_t + (size_t)pos * half;
+  const float* src;   // the dr dims to rotate
+  T* dst;             // where they go
+  if (it < H) {
+    const float* qh = row + (size_t)it * (dn + dr);
+    T* qp = q_plain + ((size_t)t * H + it) * dn;
+    for (int i = lane; i < dn; i += 32) qp[i] = from_f32<T>(qh[i]);
+    src = qh + dn;
+    dst = q_full + ((size_t)t * H + it) * (r + dr) + r;
+  } else {
+    const int page = block_table[(size_t)slot_of_token[t] * table_stride + pos / page_tokens];
+    if (page < 0) return;   // the host never schedules this; keeps a stale table from writing out of bounds
+    const float* cp = row + (size_t)H * (dn + dr);
+    T* out = pages + ((size_t)page * page_tokens + (pos % page_tokens)) * (r + dr);
+    float ss = 0.f;
+    for (int i = lane; i < r; i += 32) ss = fmaf(cp[i], cp[i], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)r + eps);
+    for (int i = lane; i < r; i += 32) out[i] = from_f32<T>(cp[i] * inv * c_w[i]);
+    src = cp + r;
+    dst = out + r;
+  }
+  for (int i = lane; i < half; i += 32) {
+    const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+    const float a = src[ia], b = src[ib];
+    dst[ia] = from_f32<T>(a * c[i] - b * s[i]);
+    dst[ib] = from_f32<T>(a * s[i] + b * c[i]);
+  }
+  for (int i = rot + lane; i < dr; i += 32) dst[i] = from_f32<T>(src[i]);
+}
+
+HK_API int hk_latent_prep(const float* proj, long long ld, void* q_plain, void* q_full, int dtype, const float* c_w, float eps,
+                          const float* cos_t, const float* sin_t, int rot, int pairing, const int* positions,
+                          const int* slot_of_token, const int* block_table, int table_stride, void* pages, int n, int H, int dn,
+                          int dr, int r, int page_tokens, int write_kv, void* stream) {
+  if (n <= 0) return 0;
+  if (rot < 0 || rot > dr || (rot & 1) || pairing < 0 || pairing > 1 || H < 1 || dn < 1 || dr < 0 || r < 1) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long items = (long long)n * (H + (write_kv ? 1 : 0));
+  const dim3 grid((unsigned)((items + 3) / 4)), block(128);
+  if (dtype == HK_F32)
+    return hk_launch_pdl(latent_prep_kernel<float>, grid, block, 0, s, proj, ld, (float*)q_plain, (float*)q_full, c_w, eps, cos_t,
+                         sin_t, rot, pairing, positions, slot_of_token, block_table, table_stride, (float*)pages, n, H, dn, dr, r,
+                         page_tokens, write_kv);
+  if (dtype == HK_BF16)
+    return hk_launch_pdl(latent_prep_kernel<bf16>, grid, block, 0, s, proj, ld, (bf16*)q_plain, (bf16*)q_full, c_w, eps, cos_t,
+                         sin_t, rot, pairing, positions, slot_of_token, block_table, table_stride, (bf16*)pages, n, H, dn, dr, r,
+                         page_tokens, write_kv);
   return HK_ERR_UNSUPPORTED;
 }

@@ -160,7 +160,7 @@ def stream_wanted(M: int, N: int, K: int) -> bool:
 
 
 def run_stream(a, w, out, epilogue: int, ldo: int) -> bool:
-    """The persistent streaming kernel; epilogue 0 store, 1 add, 2 silu(gate) * up over w = [gate rows | up rows]."""
+    """The persistent streaming kernel; epilogue 0 store, 1 add, 2 silu(gate) * up (3: tanh gelu) over w = [gate rows | up rows]."""
     from . import ops
     M, K = a.shape
     N = w.shape[0]
@@ -221,16 +221,18 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
     return True
 
 
-def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None) -> bool:
-    """out (bf16 [M, F]) = silu(gate) * up of a w^T for w = [F gate rows | F up rows], in the epilogue of the
-    streaming kernel (few rows) or of the tcgen05 kernel; False when they refuse."""
+def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None, act: int = 0) -> bool:
+    """out (bf16 [M, F]) = act(gate) * up of a w^T for w = [F gate rows | F up rows], in the epilogue of the
+    streaming kernel (few rows) or of the tcgen05 kernel; act 0 is silu, 1 the tanh form of gelu.  False when they
+    refuse."""
+    epilogue = 2 + int(act)
     from . import ops
     M, K = a.shape
     N = w_gate_up.shape[0]
     if not _aligned(a, w_gate_up) or N % 2:
         return False
     if choice == "stream" or (choice is None and stream_wanted(M, N, K)):
-        if N % (16 * stream_row_warps(N, _sms(a.device))) == 0 and run_stream(a, w_gate_up, out, 2, out.shape[1]):
+        if N % (16 * stream_row_warps(N, _sms(a.device))) == 0 and run_stream(a, w_gate_up, out, epilogue, out.shape[1]):
             return True
         if choice == "stream":
             return False
@@ -239,7 +241,7 @@ def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None) -> bool:
     lib = build.load("gemm_tc")
     bn, splits = tc_config(M, N, K, _sms(a.device), swiglu=True)
     partial = _tc_partial(lib, M, N, splits, a.device)
-    code = lib.hk_gemm_tc(_ptr(a), _ptr(w_gate_up), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), 2, bn,
+    code = lib.hk_gemm_tc(_ptr(a), _ptr(w_gate_up), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), epilogue, bn,
                           splits, _ptr(partial) if splits > 1 else ctypes.c_void_p(0), _ptr(status_flag(a.device)), _stream())
     if code == _UNSUPPORTED:
         return False

@@ -80,3 +80,78 @@ HK_API int hk_gemm_generic(const void* a, const void* w, int dtype, float* out, 
     return HK_ERR_UNSUPPORTED;
   return hk_launch_status();
 }
+
+// ----------------------------------------------------------------------------- one small product per head
+// out[t, h, :N] = a[t, h, :K] * w[h]^T for every head h: w is [heads][N][K]; a's and out's rows of one token lie
+// `lda` / `ldo` elements apart and their heads `a_head` / `o_head` elements apart (so the output may be a column
+// slice of wider rows).  The output takes the storage type or fp32.  Same tiles and summation order as above, the
+// head in blockIdx.z.
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+gemm_heads_kernel(const T* __restrict__ a, const T* __restrict__ w, TO* __restrict__ out, int M, int N, int K,
+                  long long lda, long long a_head, long long ldo, long long o_head) {
+  __shared__ float As[GG_BK][GG_BM + 4];
+  __shared__ float Ws[GG_BK][GG_BN + 4];
+  const int tid = threadIdx.x, h = blockIdx.z;
+  const int m0 = blockIdx.y * GG_BM, n0 = blockIdx.x * GG_BN;
+  const int tx = tid & 15, ty = tid >> 4;
+  a += (size_t)h * a_head;
+  w += (size_t)h * N * K;
+  out += (size_t)h * o_head;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += GG_BK) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int i = tid + j * 256;
+      int r = i >> 4, c = i & 15;
+      int gm = m0 + r, gn = n0 + r, gk = k0 + c;
+      As[c][r] = (gm < M && gk < K) ? to_f32<T>(a[(size_t)gm * lda + gk]) : 0.f;
+      Ws[c][r] = (gn < N && gk < K) ? to_f32<T>(w[(size_t)gn * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GG_BK; ++kk) {
+      float av[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wv[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int gn = n0 + tx * 4 + j;
+      if (gn < N) out[(size_t)gm * ldo + gn] = from_f32<TO>(acc[i][j]);
+    }
+  }
+}
+
+HK_API int hk_gemm_heads(const void* a, const void* w, int dtype, void* out, int out_dtype, int M, int N, int K, int heads,
+                         long long lda, long long a_head, long long ldo, long long o_head, void* stream) {
+  if (M <= 0 || N <= 0 || heads <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid((N + GG_BN - 1) / GG_BN, (M + GG_BM - 1) / GG_BM, heads);
+  if (grid.y > 65535 || grid.z > 65535) return HK_ERR_UNSUPPORTED;
+  if (dtype == HK_F32 && out_dtype == HK_F32)
+    gemm_heads_kernel<float, float><<<grid, 256, 0, s>>>((const float*)a, (const float*)w, (float*)out, M, N, K, lda, a_head, ldo, o_head);
+  else if (dtype == HK_BF16 && out_dtype == HK_BF16)
+    gemm_heads_kernel<bf16, bf16><<<grid, 256, 0, s>>>((const bf16*)a, (const bf16*)w, (bf16*)out, M, N, K, lda, a_head, ldo, o_head);
+  else if (dtype == HK_BF16 && out_dtype == HK_F32)
+    gemm_heads_kernel<bf16, float><<<grid, 256, 0, s>>>((const bf16*)a, (const bf16*)w, (float*)out, M, N, K, lda, a_head, ldo, o_head);
+  else
+    return HK_ERR_UNSUPPORTED;
+  return hk_launch_status();
+}

@@ -48,7 +48,15 @@ constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr int SMEM_BUDGET = 152 * 1024;
 constexpr int SMEM_BUDGET_WIDE = 200 * 1024;     // 17 to 32 rows: a stage is 48 KB, and three must fit
 
-enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_GEGLU = 3 };
+// The two gated epilogues differ in the gate's activation alone: silu, or the tanh form of gelu, which is
+// g * sigmoid(2 * sqrt(2 / pi) * (g + 0.044715 g^3)).
+#define IS_GLU(e) ((e) == EPI_SWIGLU || (e) == EPI_GEGLU)
+template <int EPI>
+__device__ __forceinline__ float glu_gate(float g) {
+  const float z = EPI == EPI_GEGLU ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+  return g / (1.0f + __expf(-z));
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -134,7 +142,7 @@ struct Control {
 // [F gate rows | F up rows]; the first half are gate rows, the second their up rows, F further down.
 template <int BN, int EPI>
 __device__ __forceinline__ int tile_row(int tile, int half, int F) {
-  if (EPI == EPI_SWIGLU) return tile * (BN / 2) + half * F;
+  if (IS_GLU(EPI)) return tile * (BN / 2) + half * F;
   return tile * BN + half * (BN / 2);
 }
 
@@ -245,13 +253,13 @@ __device__ __forceinline__ void consume_units(const Sched& sc, uint32_t i_base, 
         return s;
       };
       auto finish = [&](auto value) {
-        if (EPI == EPI_SWIGLU) {
+        if (IS_GLU(EPI)) {
           const int f0 = tile * (BN / 2);
           for (int e = tid; e < (BN / 2) * COLS; e += CONSUMERS * 32) {
             const int m = e / (BN / 2), row = e % (BN / 2);
             if (m >= M) continue;
             const float gate = value(m * BN + row), up = value(m * BN + row + BN / 2);
-            reinterpret_cast<bf16*>(out)[(size_t)m * ldo + f0 + row] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+            reinterpret_cast<bf16*>(out)[(size_t)m * ldo + f0 + row] = __float2bfloat16_rn(glu_gate<EPI>(gate) * up);
           }
         } else {
           const int n0 = tile * BN;
@@ -333,7 +341,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   volatile int* abort_flag = &ctl->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const Sched sc = make_sched(EPI == EPI_SWIGLU ? N / BN : (N + BN - 1) / BN, (K + BK - 1) / BK, gridDim.x, blockIdx.x);
+  const Sched sc = make_sched(IS_GLU(EPI) ? N / BN : (N + BN - 1) / BN, (K + BK - 1) / BK, gridDim.x, blockIdx.x);
   const int kc = sc.kc, ns = sc.ns, n_local = sc.n_local, own_first = sc.own_first;
   const long long u0 = sc.u0;
 
@@ -432,7 +440,7 @@ int launch(const void* a, const void* w, void* out, int M, int N, int K, long lo
   if (!make_map(&ma, a, M, K, 8 * MT, S::KW) || !make_map(&mw, w, N, K, S::BN / 2, S::KW)) return HK_ERR_UNSUPPORTED;
   static HkSmemCache allowed = {};
   if (int e = hk_allow_smem(gemm_stream_kernel<RW, MT, EPI>, (size_t)S::SMEM, allowed)) return e;
-  const int n_tiles = EPI == EPI_SWIGLU ? N / S::BN : (N + S::BN - 1) / S::BN;
+  const int n_tiles = IS_GLU(EPI) ? N / S::BN : (N + S::BN - 1) / S::BN;
   const long long units = (long long)n_tiles * ((K + S::BK - 1) / S::BK);
   long long grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
@@ -446,14 +454,15 @@ int launch_epi(int epilogue, const void* a, const void* w, void* out, int M, int
                int* counters, int* status, int max_ctas, cudaStream_t s) {
   if (epilogue == EPI_STORE) return launch<RW, MT, EPI_STORE>(a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s);
   if (epilogue == EPI_ADD) return launch<RW, MT, EPI_ADD>(a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s);
+  if (epilogue == EPI_GEGLU) return launch<RW, MT, EPI_GEGLU>(a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s);
   return launch<RW, MT, EPI_SWIGLU>(a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s);
 }
 
 
 }  // namespace
 
-// out = a w^T for M <= 32.  epilogue 0: out fp32 [M, N] stored; 1: out fp32 [M, N] +=; 2: out bf16 [M, N/2] =
-// silu(gate) * up with w = [N/2 gate rows | N/2 up rows] (N a multiple of the tile's rows, 16 * rw).
+// out = a w^T for M <= 32.  epilogue 0: out fp32 [M, N] stored; 1: out fp32 [M, N] +=; 2 (silu) or 3 (tanh gelu): out bf16 [M, N/2] =
+// act(gate) * up with w = [N/2 gate rows | N/2 up rows] (N a multiple of the tile's rows, 16 * rw).
 // rw: 8, 4, 2 or 1 consumer warps across a tile's rows (tiles of 128, 64, 32 or 16 rows; the other warps split K).
 // workspace: at least hk_gemm_stream_workspace(M, rw) floats; counters: one int per tile of 16 rows of w, zero
 // before the first launch (left zero); status: device int that a timed-out wait sets to 1.
@@ -463,7 +472,7 @@ HK_API int hk_gemm_stream(const void* a, const void* w, void* out, int M, int N,
                           float* workspace, int* counters, int* status, int max_ctas, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 32 || K <= 0 || (K & 63) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return HK_ERR_UNSUPPORTED;
-  if (epilogue < 0 || epilogue > 2 || (epilogue == EPI_SWIGLU && (rw < 1 || N % (16 * rw)))) return HK_ERR_UNSUPPORTED;
+  if (epilogue < 0 || epilogue > 3 || (IS_GLU(epilogue) && (rw < 1 || N % (16 * rw)))) return HK_ERR_UNSUPPORTED;
   if (workspace == nullptr || counters == nullptr || status == nullptr) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   const int mt = M <= 8 ? 1 : M <= 16 ? 2 : 4;

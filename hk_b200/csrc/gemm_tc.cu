@@ -40,7 +40,15 @@ constexpr int RING_BYTES = 227 * 1024 - 2 * 1024;   // what is left of an SM's s
 constexpr uint32_t TMEM_COLS = 2 * MAX_BN;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
-enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_GEGLU = 3 };
+// The two gated epilogues differ in the gate's activation alone: silu, or the tanh form of gelu, which is
+// g * sigmoid(2 * sqrt(2 / pi) * (g + 0.044715 g^3)).
+#define IS_GLU(e) ((e) == EPI_SWIGLU || (e) == EPI_GEGLU)
+template <int EPI>
+__device__ __forceinline__ float glu_gate(float g) {
+  const float z = EPI == EPI_GEGLU ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+  return g / (1.0f + __expf(-z));
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -193,7 +201,7 @@ __device__ __forceinline__ void load_chunk(const float* o, int c0, float4* y) {
 }
 
 // W gate columns at c0 and their up columns `h` further on -> W bf16 outputs silu(gate) * up.
-template <int W>
+template <int W, int EPI>
 __device__ __forceinline__ void swiglu_chunk(uint32_t taddr, bf16* o, int c0, int h, int n_out, bool row_ok, bool vec_ok) {
   uint32_t g[W], u[W];
   tmem_ld<W>(taddr + (uint32_t)c0, g);
@@ -207,8 +215,8 @@ __device__ __forceinline__ void swiglu_chunk(uint32_t taddr, bf16* o, int c0, in
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
-        float h0 = g0 / (1.0f + __expf(-g0)) * __uint_as_float(u[j + 2 * e]);
-        float h1 = g1 / (1.0f + __expf(-g1)) * __uint_as_float(u[j + 2 * e + 1]);
+        float h0 = glu_gate<EPI>(g0) * __uint_as_float(u[j + 2 * e]);
+        float h1 = glu_gate<EPI>(g1) * __uint_as_float(u[j + 2 * e + 1]);
         __nv_bfloat162 p = __floats2bfloat162_rn(h0, h1);
         packed[e] = *reinterpret_cast<uint32_t*>(&p);
       }
@@ -218,7 +226,7 @@ __device__ __forceinline__ void swiglu_chunk(uint32_t taddr, bf16* o, int c0, in
     for (int j = 0; j < W; ++j)
       if (c0 + j < n_out) {
         float gv = __uint_as_float(g[j]);
-        o[c0 + j] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * __uint_as_float(u[j]));
+        o[c0 + j] = __float2bfloat16_rn(glu_gate<EPI>(gv) * __uint_as_float(u[j]));
       }
   }
 }
@@ -240,7 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = bn >> 1, F = N >> 1;
   const int m_tiles = (M + BM - 1) / BM;
-  const int n_tiles = EPI == EPI_SWIGLU ? (F + h - 1) / h : (N + bn - 1) / bn;
+  const int n_tiles = IS_GLU(EPI) ? (F + h - 1) / h : (N + bn - 1) / bn;
   // With splits > 1 a work item is (output tile, slice of K); slice s of every tile comes before slice s + 1
   // of any, so the CTAs running together read different weights.  Each item stores its fp32 partial to
   // partial[s][M][N] (slices `slice_floats` apart); a second kernel adds the slices in order.
@@ -292,7 +300,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           uint8_t* st = ring + (size_t)stage * stage_bytes;
           mbar_expect_tx(&sm.full[stage], tx_bytes);
           tma_load_2d(st, &map_a, &sm.full[stage], kb * BK, m0);
-          if (EPI == EPI_SWIGLU) {
+          if (IS_GLU(EPI)) {
             tma_load_2d(st + A_BYTES, &map_w, &sm.full[stage], kb * BK, w0 + nt * h);
             tma_load_2d(st + A_BYTES + h * (BK * 2), &map_w, &sm.full[stage], kb * BK, w0 + F + nt * h);
           } else {
@@ -378,14 +386,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll 1
         for (; c0 + 32 <= bn; c0 += 32) store_chunk<32, false>(taddr, o, c0, n_out, row_ok, vec_ok);
         if (c0 < bn) store_chunk<16, false>(taddr, o, c0, n_out, row_ok, vec_ok);
-      } else if (EPI == EPI_SWIGLU) {
+      } else if (IS_GLU(EPI)) {
         bf16* o = reinterpret_cast<bf16*>(out) + (size_t)row * ldo + nt * h;
         const int n_out = F - nt * h;
         const bool vec_ok = (ldo & 7) == 0 && ((nt * h) & 7) == 0;
         int c0 = 0;
 #pragma unroll 1
-        for (; c0 + 32 <= h; c0 += 32) swiglu_chunk<32>(taddr, o, c0, h, n_out, row_ok, vec_ok);
-        if (c0 < h) swiglu_chunk<16>(taddr, o, c0, h, n_out, row_ok, vec_ok);
+        for (; c0 + 32 <= h; c0 += 32) swiglu_chunk<32, EPI>(taddr, o, c0, h, n_out, row_ok, vec_ok);
+        if (c0 < h) swiglu_chunk<16, EPI>(taddr, o, c0, h, n_out, row_ok, vec_ok);
       } else {
         const int n0 = nt * bn;
         float* o = reinterpret_cast<float*>(out) + (size_t)row * ldo + n0;
@@ -466,17 +474,17 @@ int sm_count() {
 }
 
 // Adds the K slices of a split product in slice order.  mode 0: out fp32 = sum; 1: out fp32 += sum;
-// 2: out bf16 [M, N/2] = silu(gate) * up, the partial sums' columns in tiles of [bn / 2 gates | their bn / 2 ups].
+// 2 (silu) and 3 (tanh gelu): out bf16 [M, N/2] = act(gate) * up, the partial sums' columns in tiles of [bn / 2 gates | their bn / 2 ups].
 template <int MODE>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int M, int N, long long ldo,
                                      int splits, int bn) {
-  const long long total = MODE == 2 ? (long long)M * (N / 2) : (long long)M * N;
+  const long long total = MODE >= 2 ? (long long)M * (N / 2) : (long long)M * N;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();          // the partial sums come from the kernel before
   if (i >= total) return;
   const size_t slice = slice_floats(M, N);
-  if (MODE == 2) {
+  if (MODE >= 2) {
     const int F = N / 2;
     const int m = (int)(i / F), j = (int)(i % F);
     const int h = bn >> 1;
@@ -486,7 +494,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
       gsum += partial[s * slice + gi];
       usum += partial[s * slice + gi + h];
     }
-    reinterpret_cast<bf16*>(out)[(size_t)m * ldo + j] = __float2bfloat16_rn(gsum / (1.0f + __expf(-gsum)) * usum);
+    reinterpret_cast<bf16*>(out)[(size_t)m * ldo + j] = __float2bfloat16_rn(glu_gate<MODE>(gsum) * usum);
   } else {
     const int m = (int)(i / N), n = (int)(i % N);
     float sum = 0.f;
@@ -531,18 +539,18 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   const size_t smem = (size_t)stages * stage_bytes + CONTROL_BYTES + 1024;
   if (int e = hk_allow_smem(gemm_tc_kernel<EPI>, smem, allowed)) return e;
-  const int n_tiles = EPI == EPI_SWIGLU ? (N / 2 + bn / 2 - 1) / (bn / 2) : (N + bn - 1) / bn;
+  const int n_tiles = IS_GLU(EPI) ? (N / 2 + bn / 2 - 1) / (bn / 2) : (N + bn - 1) / bn;
   const int tiles = ((M + BM - 1) / BM) * n_tiles * splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   // dependent launches (measured over decode steps of 24 and 64 rows: 1 % faster; the kernels after this one set up while it drains)
   int code = hk_launch_pdl(gemm_tc_kernel<EPI>, dim3(grid), dim3(NUM_THREADS), smem, s, ma, mw, out, M, N, K, ldo, bn, stages, splits, partial, status, groups);
   if (code != 0 || splits <= 1) return code;
-  if (EPI != EPI_SWIGLU && (N & 3) == 0 && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0) {
+  if (!IS_GLU(EPI) && (N & 3) == 0 && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0) {
     const long long quads = (long long)M * (N / 4);
     return hk_launch_pdl(splitk_reduce_vec_kernel<EPI == EPI_ADD ? 1 : 0>, dim3((unsigned)((quads + 127) / 128)), dim3(128), 0, s,
                          (const float*)partial, reinterpret_cast<float*>(out), M, N, ldo, splits);
   }
-  const long long total = EPI == EPI_SWIGLU ? (long long)M * (N / 2) : (long long)M * N;
+  const long long total = IS_GLU(EPI) ? (long long)M * (N / 2) : (long long)M * N;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   return hk_launch_pdl(splitk_reduce_kernel<EPI>, dim3(blocks), dim3(256), 0, s, (const float*)partial, out, M, N, ldo, splits, bn);
 }
@@ -561,16 +569,17 @@ HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int
                       int splits, float* partial, int* status, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return HK_ERR_UNSUPPORTED;
-  if (epilogue < EPI_STORE || epilogue > EPI_SWIGLU) return HK_ERR_UNSUPPORTED;
+  if (epilogue < EPI_STORE || epilogue > EPI_GEGLU) return HK_ERR_UNSUPPORTED;
   if (bn < 16 || bn > MAX_BN || (bn & 15)) return HK_ERR_UNSUPPORTED;
-  if (epilogue == EPI_SWIGLU && ((N & 1) || (bn & 31))) return HK_ERR_UNSUPPORTED;
+  if (IS_GLU(epilogue) && ((N & 1) || (bn & 31))) return HK_ERR_UNSUPPORTED;
   if (splits < 1 || splits > (K + BK - 1) / BK || (splits > 1 && partial == nullptr)) return HK_ERR_UNSUPPORTED;
-  if (epilogue == EPI_SWIGLU && splits > 1 && (N / 2) % (bn / 2) != 0) return HK_ERR_UNSUPPORTED;
+  if (IS_GLU(epilogue) && splits > 1 && (N / 2) % (bn / 2) != 0) return HK_ERR_UNSUPPORTED;
   CUtensorMap ma, mw;
-  if (!make_map(&ma, a, M, K, BM) || !make_map(&mw, w, N, K, epilogue == EPI_SWIGLU ? bn / 2 : bn)) return HK_ERR_UNSUPPORTED;
+  if (!make_map(&ma, a, M, K, BM) || !make_map(&mw, w, N, K, IS_GLU(epilogue) ? bn / 2 : bn)) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   if (epilogue == EPI_STORE) return launch<EPI_STORE>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
   if (epilogue == EPI_ADD) return launch<EPI_ADD>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
+  if (epilogue == EPI_GEGLU) return launch<EPI_GEGLU>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
   return launch<EPI_SWIGLU>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
 }
 
@@ -586,10 +595,10 @@ HK_API int hk_gemm_tc_grouped(const void* a, const void* w, void* out, int M, in
   if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || (M % BM) || groups == nullptr) return HK_ERR_UNSUPPORTED;
   if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return HK_ERR_UNSUPPORTED;
   if (bn < 16 || bn > MAX_BN || (bn & 15)) return HK_ERR_UNSUPPORTED;
-  if (epilogue == EPI_SWIGLU && ((N & 1) || (bn & 31))) return HK_ERR_UNSUPPORTED;
+  if (IS_GLU(epilogue) && ((N & 1) || (bn & 31))) return HK_ERR_UNSUPPORTED;
   if ((long long)n_groups * N > 0x7fffffffLL) return HK_ERR_UNSUPPORTED;
   CUtensorMap ma, mw;
-  if (!make_map(&ma, a, M, K, BM) || !make_map(&mw, w, n_groups * N, K, epilogue == EPI_SWIGLU ? bn / 2 : bn)) return HK_ERR_UNSUPPORTED;
+  if (!make_map(&ma, a, M, K, BM) || !make_map(&mw, w, n_groups * N, K, IS_GLU(epilogue) ? bn / 2 : bn)) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   if (epilogue == EPI_STORE) return launch<EPI_STORE>(ma, mw, out, M, N, K, ldo, bn, 1, nullptr, status, s, groups);
   return launch<EPI_SWIGLU>(ma, mw, out, M, N, K, ldo, bn, 1, nullptr, status, s, groups);

@@ -105,8 +105,21 @@ def force(gemm: Optional[str] = None, attention: Optional[str] = None):
 # ---- embedding ------------------------------------------------------------------------
 
 
-def embedding(table: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = table[token_ids[t], :] widened to float32."""
+def _narrow_target(narrow: Optional[torch.Tensor], like: torch.Tensor, what: str):
+    """The optional bfloat16 copy that a row-wise kernel writes beside its float32 result."""
+    if narrow is None:
+        return None
+    _need(narrow, "narrow", torch.bfloat16, 2)
+    if narrow.shape != like.shape:
+        raise KernelError(f"{what}: the narrowed copy must have the result's shape")
+    return narrow
+
+
+def embedding(table: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
+              narrow: Optional[torch.Tensor] = None) -> None:
+    """out[t, :] = table[token_ids[t], :] widened to float32, times `scale`; `narrow` (bfloat16, out's shape) receives
+    the same rows rounded."""
+    narrow = _narrow_target(narrow, out, "embedding")
     _need(table, "table", dims=2)
     _need(token_ids, "token_ids", torch.int32, 1)
     _need(out, "out", torch.float32, 2)
@@ -114,7 +127,8 @@ def embedding(table: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor) -
     if token_ids.shape[0] != n or table.shape[1] != d:
         raise KernelError(f"embedding: out {tuple(out.shape)} does not fit ids {tuple(token_ids.shape)} and table {tuple(table.shape)}")
     lib = build.load("elementwise")
-    _check(lib.hk_embedding(_ptr(table), _dt(table), _ptr(token_ids), _ptr(out), n, d, table.shape[0], _stream()),
+    _check(lib.hk_embedding(_ptr(table), _dt(table), _ptr(token_ids), _ptr(out), n, d, table.shape[0],
+                            ctypes.c_float(scale), _ptr(narrow), _stream()),
            "embedding")
 
 
@@ -146,9 +160,14 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
 # ---- swiglu ---------------------------------------------------------------------------
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
-    """out[t, j] = silu(gate) * up for gate_up float32 [n, 2F].  With block = 0 the row is laid out
-    [F gates | F ups]; with block = b (dividing F) it is [b gates | b ups | b gates | ...]."""
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, act: str = "silu") -> None:
+    """out[t, j] = act(gate) * up for gate_up float32 [n, 2F]; act is silu or the tanh form of gelu.  With block = 0
+    the row is laid out [F gates | F ups]; with block = b (dividing F) it is [b gates | b ups | b gates | ...]."""
+    if act not in GLU_ACTS:
+        raise KernelError(f"swiglu: activation {act!r} is neither 'silu' nor 'gelu_tanh'")
     _need(gate_up, "gate_up", torch.float32, 2)
     _need(out, "out", dims=2)
     n, f = out.shape
@@ -156,7 +175,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     if gate_up.shape[0] != n or gate_up.shape[1] != 2 * f or f % block:
         raise KernelError("swiglu: gate_up must be [n, 2F] for out [n, F], and the block must divide F")
     lib = build.load("elementwise")
-    _check(lib.hk_swiglu(_ptr(gate_up), _ptr(out), _dt(out), n, f, int(block), _stream()), "swiglu")
+    _check(lib.hk_swiglu(_ptr(gate_up), _ptr(out), _dt(out), n, f, int(block), GLU_ACTS[act], _stream()), "swiglu")
 
 
 def _as_weights(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -169,8 +188,8 @@ def _as_weights(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return a.to(w.dtype)
 
 
-def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, F] = silu(gate) * up of a @ w_gate_up^T, w_gate_up [2F, K] = [F gate rows | F up rows].  Fused into
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, act: str = "silu") -> None:
+    """out[M, F] = act(gate) * up (act: silu, or the tanh form of gelu) of a @ w_gate_up^T, w_gate_up [2F, K] = [F gate rows | F up rows].  Fused into
     the tensor-core product's epilogue when that takes the shape (a tile of the product then holds gate rows and
     the up rows that match them), else a product to float32 followed by the swiglu kernel."""
     _need(a, "a", dims=2)
@@ -178,7 +197,7 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> 
     _need(out, "out", a.dtype, 2)
     if w_gate_up.dtype != a.dtype:              # weights kept in 32-bit on the bfloat16 path: this product runs in 32-bit
         wide = torch.empty(out.shape, dtype=w_gate_up.dtype, device=out.device)
-        gemm_swiglu(_as_weights(a, w_gate_up), w_gate_up, wide)
+        gemm_swiglu(_as_weights(a, w_gate_up), w_gate_up, wide, act)
         out.copy_(wide)
         return
     M, F = out.shape
@@ -186,11 +205,11 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> 
         raise KernelError("gemm_swiglu: shapes do not fit")
     if a.dtype == torch.bfloat16 and _forced["gemm"] in (None, "tc", "stream"):
         from . import gemm_fast
-        if gemm_fast.run_swiglu(a, w_gate_up, out, _forced["gemm"]):
+        if gemm_fast.run_swiglu(a, w_gate_up, out, _forced["gemm"], act=GLU_ACTS[act]):
             return
     gu = torch.empty((M, 2 * F), dtype=torch.float32, device=a.device)
     gemm(a, w_gate_up, gu)
-    swiglu(gu, out, 0)
+    swiglu(gu, out, 0, act)
 
 
 # ---- per-head norm + rotation + cache write ---------------------------------------------
@@ -202,7 +221,8 @@ PAIRINGS = {"half": 0, "adjacent": 1}
 def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_dim, positions,
                           slot_of_token, block_table, k_pages, v_pages, n_heads, n_kv_heads, head_dim,
                           page_tokens, write_kv=True, bias=None, pairing="half", norm_after=False, tied_v=False) -> None:
-    """Splits the fused projection qkv[n, (H+2G)*hd] (float32): q heads are normalised (if
+    """Splits the fused projection qkv[n, (H+G)*hd + G*vd] (float32; vd = v_pages' width, hd unless the values have a
+    width of their own): q heads are normalised (if
     q_weight), rotated (if rotary_dim > 0) and stored to q_out[n, H*hd]; k heads likewise and
     stored, with the v heads, into the token's cache page [page, G, page_tokens, hd].
     `bias` (float32 [(H+2G)*hd]) is added to the projection first.  `pairing`: "half" rotates dims
@@ -211,15 +231,18 @@ def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_
     value is its key as projected (before norm and rotation), of which the first v_pages.shape[-1] dims are kept."""
     if pairing not in PAIRINGS:
         raise KernelError(f"qk_norm_rope_kv_write: pairing {pairing!r} is neither 'half' nor 'adjacent'")
-    if bias is not None:
-        _need(bias, "bias", torch.float32, 1)
-        if bias.shape[0] != (n_heads + (1 if tied_v else 2) * n_kv_heads) * head_dim:
-            raise KernelError("qk_norm_rope_kv_write: bias must have one entry per projected column")
-    _need(qkv, "qkv", torch.float32, 2)
+    if not isinstance(qkv, torch.Tensor) or not qkv.is_cuda or qkv.dtype != torch.float32 or qkv.dim() != 2 or qkv.stride(1) != 1:
+        raise KernelError("qkv must be a float32 CUDA matrix with unit column stride (it may be a column slice)")
     _need(q_out, "q_out", dims=2)
     n = qkv.shape[0]
     H, G, hd = n_heads, n_kv_heads, head_dim
-    if qkv.shape[1] != (H + (1 if tied_v else 2) * G) * hd or tuple(q_out.shape) != (n, H * hd):
+    vd = int(v_pages.shape[3]) if write_kv else (hd if tied_v else (qkv.shape[1] - (H + G) * hd) // max(G, 1))
+    width = (H + G) * hd + (0 if tied_v else G * vd)
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != width:
+            raise KernelError("qk_norm_rope_kv_write: bias must have one entry per projected column")
+    if qkv.shape[1] != width or tuple(q_out.shape) != (n, H * hd):
         raise KernelError("qk_norm_rope_kv_write: qkv or q_out has the wrong shape")
     if head_dim > 256:
         raise KernelError(f"qk_norm_rope_kv_write: head_dim {head_dim} is above 256")
@@ -240,9 +263,8 @@ def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_
         _need(k_pages, "k_pages", q_out.dtype, 4)
         _need(v_pages, "v_pages", q_out.dtype, 4)
         if tuple(k_pages.shape[1:]) != (G, page_tokens, hd) or tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3]) \
-                or not 1 <= v_pages.shape[3] <= hd or (v_pages.shape[3] != hd and not tied_v):
-            raise KernelError("cache pages must be [pages, G, page_tokens, head_dim]")
-    vd = int(v_pages.shape[3]) if write_kv else hd
+                or not 1 <= v_pages.shape[3] <= 256 or (v_pages.shape[3] > hd and tied_v):
+            raise KernelError("cache pages must be [pages, G, page_tokens, head_dim] (values: their own width)")
     lib = build.load("elementwise")
     _check(lib.hk_qk_norm_rope_kv_write(
         _ptr(qkv), _ptr(q_out), _dt(q_out), _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps),
@@ -250,7 +272,7 @@ def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_
         _ptr(positions), _ptr(slot_of_token), _ptr(block_table if write_kv else None),
         int(block_table.shape[1]) if write_kv else 0, _ptr(k_pages if write_kv else None),
         _ptr(v_pages if write_kv else None), n, H, G, hd, int(page_tokens), 1 if write_kv else 0, _ptr(bias),
-        PAIRINGS[pairing], 1 if norm_after else 0, 1 if tied_v else 0, vd, _stream()),
+        PAIRINGS[pairing], 1 if norm_after else 0, 1 if tied_v else 0, vd, ctypes.c_longlong(qkv.stride(0)), _stream()),
         "qk_norm_rope_kv_write")
 
 
@@ -300,33 +322,51 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool =
 
 
 def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, out, n_heads, n_kv_heads,
-                    head_dim, page_tokens, window: int, scale: float, plan=None, sink: bool = False) -> None:
+                    head_dim, page_tokens, window: int, scale: float, plan=None, sink: bool = False, sinks=None,
+                    softcap: float = 0.0, chunk: int = 0, gate=None) -> None:
     """out[t, h, :] = softmax_j(scale * q[t, h] . k[j]) v[j] over the keys j in
     [max(0, p - window + 1), p] (all of [0, p] when window <= 0) of the token's request, read
     through its block-table row; p = positions[t].  `plan` carries the per-request tiling the
-    flash kernel wants; without it (or for sizes it refuses) the generic kernel runs.  Values may be narrower than
-    keys (v_pages [pages, G, page_tokens, vd], out [n, H*vd]; generic kernel).  `sink`: one more term in the softmax's
-    denominator, a key of score 0 without a value: p_j = exp(s_j) / (1 + sum exp(s_j))."""
+    flash kernel wants; without it (or for sizes it refuses) the generic kernel runs.  Values may have a width of
+    their own (v_pages [pages, G, page_tokens, vd], out [n, H*vd]; generic kernel).  `v_pages` None: the cache keeps
+    one tensor per token and a token's value is the first vd = out.shape[1] / H dims of its key row.
+    `sink`: one more term in the softmax's denominator, a key without a value whose score is 0, or `sinks[h]` when
+    that float32 [H] tensor is given: p_j = exp(s_j) / (exp(sink) + sum exp(s_j)).
+    `softcap` c > 0: scores become c * tanh(score / c).  `chunk` s > 0: a token sees no key before the start of its own
+    block of s positions.  `gate` (a float32 column slice [n, H*vd] of a projection's output): the result is
+    multiplied by sigmoid(gate)."""
     _need(q, "q", dims=2)
     _need(out, "out", q.dtype, 2)
     _need(k_pages, "k_pages", q.dtype, 4)
-    _need(v_pages, "v_pages", q.dtype, 4)
+    if v_pages is not None:
+        _need(v_pages, "v_pages", q.dtype, 4)
     _need(block_table, "block_table", torch.int32, 2)
     _need(positions, "positions", torch.int32, 1)
     _need(slot_of_token, "slot_of_token", torch.int32, 1)
     n = q.shape[0]
     H, G, hd = n_heads, n_kv_heads, head_dim
-    vd = int(v_pages.shape[3])
+    if H < 1 or G < 1 or H % G != 0:
+        raise KernelError(f"paged_attention: {H} heads are not a multiple of {G} groups")
+    vd = int(v_pages.shape[3]) if v_pages is not None else int(out.shape[1]) // H
     if tuple(q.shape) != (n, H * hd) or tuple(out.shape) != (n, H * vd):
         raise KernelError("paged_attention: q must be [n, H*head_dim] and out [n, H*value_dim]")
-    if tuple(k_pages.shape[1:]) != (G, page_tokens, hd) or tuple(k_pages.shape[:3]) != tuple(v_pages.shape[:3]) or not 1 <= vd <= hd:
+    if tuple(k_pages.shape[1:]) != (G, page_tokens, hd) or (v_pages is not None and tuple(k_pages.shape[:3]) != tuple(v_pages.shape[:3])) \
+            or vd < 1 or (v_pages is None and vd > hd):
         raise KernelError("paged_attention: cache pages must be [pages, G, page_tokens, head_dim]")
-    if H % G != 0:
-        raise KernelError(f"paged_attention: {H} heads are not a multiple of {G} groups")
-    if hd > 256:
-        raise KernelError(f"paged_attention: head_dim {hd} is above 256")
+    if max(hd, vd) > 640:
+        raise KernelError(f"paged_attention: a head of {max(hd, vd)} dims is above 640")
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, 1)
+        if sinks.shape[0] != H or not sink:
+            raise KernelError("paged_attention: sinks must hold one score per query head (and sink be set)")
+    gate_ld = 0
+    if gate is not None:
+        gate_ld = _cols(gate, "gate", H * vd)
+        if gate.shape[0] != n:
+            raise KernelError("paged_attention: one row of gate logits per token")
     choice = _forced["attention"]
-    if q.dtype == torch.bfloat16 and choice != "generic" and plan is not None and vd == hd:
+    plain = v_pages is not None and vd == hd and sinks is None and not softcap and not chunk and gate is None
+    if q.dtype == torch.bfloat16 and choice != "generic" and plan is not None and plain:
         from . import attention_fast
         if attention_fast.run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan,
                               allow_tma=choice != "flash_cp", sink=sink):
@@ -335,9 +375,83 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
             raise KernelError(f"paged_attention: the '{choice}' kernel refuses head_dim={hd} page_tokens={page_tokens}")
     lib = build.load("attention_generic")
     _check(lib.hk_attention_generic(
-        _ptr(q), _ptr(k_pages), _ptr(v_pages), _dt(q), _ptr(block_table), int(block_table.shape[1]),
-        _ptr(positions), _ptr(slot_of_token), _ptr(out), n, H, G, hd, int(page_tokens), int(window),
-        ctypes.c_float(scale), vd, 1 if sink else 0, _stream()), "paged_attention")
+        _ptr(q), _ptr(k_pages), _ptr(v_pages if v_pages is not None else k_pages), _dt(q), _ptr(block_table),
+        int(block_table.shape[1]), _ptr(positions), _ptr(slot_of_token), _ptr(out), n, H, G, hd, int(page_tokens), int(window),
+        ctypes.c_float(scale), vd, 1 if sink else 0, _ptr(sinks), ctypes.c_float(softcap), int(chunk),
+        vd if v_pages is not None else hd, _ptr(gate), ctypes.c_longlong(gate_ld), _stream()), "paged_attention")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x * sigmoid(gate) element by element; x [n, W] float32 or out's type, gate a float32 column slice [n, W] of
+    a projection's output (any row stride)."""
+    _need(x, "x", dims=2)
+    _need(out, "out", dims=2)
+    n, W = out.shape
+    ld = _cols(gate, "gate", W)
+    if x.shape != out.shape or gate.shape[0] != n or (x.dtype != torch.float32 and x.dtype != out.dtype):
+        raise KernelError("sigmoid_gate: shapes or types do not fit")
+    lib = build.load("elementwise")
+    _check(lib.hk_sigmoid_gate(_ptr(x), _dt(x), _ptr(gate), ctypes.c_longlong(ld), _ptr(out), _dt(out), n, W, _stream()),
+           "sigmoid_gate")
+
+
+def latent_prep(proj, q_plain, q_full, c_weight, eps, cos, sin, rotary_dim, pairing, positions, slot_of_token, block_table,
+                pages, n_heads, plain_dim, rot_dim, rank, page_tokens, write_kv=True) -> None:
+    """What a token brings to a latent attention, from the fused projection proj float32 [n, >= H*(dn+dr) + r + dr]
+    = [H query heads of (dn plain | dr to rotate) | r compressed dims | dr dims of the shared rotated key | ...]:
+    q_plain[n, H*dn] takes the queries' plain parts, q_full[n, H*(r+dr)] their rotated parts in its last dr dims per
+    head (the first r are left for the absorbed product), and the token's cache row [page, 0, place, r+dr] takes the
+    compressed dims RMS-normed with `c_weight` and the rotated key part."""
+    if pairing not in PAIRINGS:
+        raise KernelError(f"latent_prep: pairing {pairing!r} is neither 'half' nor 'adjacent'")
+    H, dn, dr, r = n_heads, plain_dim, rot_dim, rank
+    _need(q_plain, "q_plain", dims=2)
+    _need(q_full, "q_full", q_plain.dtype, 2)
+    _need(c_weight, "c_weight", torch.float32, 1)
+    n = q_plain.shape[0]
+    if not isinstance(proj, torch.Tensor) or not proj.is_cuda or proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1 \
+            or proj.shape[0] != n or proj.shape[1] < H * (dn + dr) + r + dr:
+        raise KernelError("latent_prep: the projection must be float32 [n, >= H*(dn+dr) + r + dr] with unit column stride")
+    if tuple(q_plain.shape) != (n, H * dn) or tuple(q_full.shape) != (n, H * (r + dr)) or c_weight.shape[0] != r:
+        raise KernelError("latent_prep: q_plain, q_full or the norm weight has the wrong shape")
+    if rotary_dim > 0:
+        _need(cos, "cos", torch.float32, 2)
+        _need(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape or rotary_dim % 2 or rotary_dim > dr:
+            raise KernelError("rotation tables must be [positions, rotary_dim/2]")
+    _need(positions, "positions", torch.int32, 1)
+    _need(slot_of_token, "slot_of_token", torch.int32, 1)
+    if write_kv:
+        _need(block_table, "block_table", torch.int32, 2)
+        _need(pages, "pages", q_plain.dtype, 4)
+        if tuple(pages.shape[1:]) != (1, page_tokens, r + dr):
+            raise KernelError("latent_prep: cache pages must be [pages, 1, page_tokens, rank + rot_dim]")
+    lib = build.load("elementwise")
+    _check(lib.hk_latent_prep(
+        _ptr(proj), ctypes.c_longlong(proj.stride(0)), _ptr(q_plain), _ptr(q_full), _dt(q_plain), _ptr(c_weight),
+        ctypes.c_float(eps), _ptr(cos if rotary_dim > 0 else None), _ptr(sin if rotary_dim > 0 else None), int(rotary_dim),
+        PAIRINGS[pairing], _ptr(positions), _ptr(slot_of_token), _ptr(block_table if write_kv else None),
+        int(block_table.shape[1]) if write_kv else 0, _ptr(pages if write_kv else None), n, H, dn, dr, r, int(page_tokens),
+        1 if write_kv else 0, _stream()), "latent_prep")
+
+
+def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_heads: int) -> None:
+    """One small product per head: out[t, h, :N] = a[t, h, :K] @ w[h]^T for w [H, N, K].  `a` and `out` are 3-D views
+    [n, H, K] and [n, H, N] with any row and head strides and unit stride along the last dimension (so either may be
+    a slice of wider heads).  out takes a's type or float32."""
+    H = n_heads
+    for name, t in (("a", a), ("out", out)):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dim() != 3 or t.stride(2) != 1 or t.shape[1] != H:
+            raise KernelError(f"gemm_heads: {name} must be a CUDA view [n, heads, width] with unit stride along the width")
+    _need(w, "w", a.dtype, 3)
+    n, _, K = a.shape
+    N = out.shape[2]
+    if tuple(w.shape) != (H, N, K) or out.shape[0] != n:
+        raise KernelError("gemm_heads: shapes do not fit")
+    lib = build.load("gemm_generic")
+    _check(lib.hk_gemm_heads(_ptr(a), _ptr(w), _dt(a), _ptr(out), _dt(out), n, N, K, H, ctypes.c_longlong(a.stride(0)),
+                             ctypes.c_longlong(a.stride(1)), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)),
+                             _stream()), "gemm_heads")
 
 
 # ---- sampling -------------------------------------------------------------------------
@@ -391,17 +505,20 @@ def sample(logits, temperature, top_k, top_p, min_p, seeds, counters, out) -> No
 # ---- a layer that norms both sides of its sublayers --------------------------------------
 
 
-def rms_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor) -> None:
+def rms_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor,
+                 narrow: Optional[torch.Tensor] = None) -> None:
     """residual[r, :] += y[r, :] * rsqrt(mean(y^2) + eps) * weight (all float32): the norm behind a sublayer, fused
-    with the residual sum."""
+    with the residual sum.  `narrow` (bfloat16, residual's shape) receives the new residual rounded: the next
+    sublayer's input where sublayers read the residual stream itself."""
+    narrow = _narrow_target(narrow, residual, "rms_norm_add")
     _need(y, "y", torch.float32, 2)
     _need(weight, "weight", torch.float32, 1)
     _need(residual, "residual", torch.float32, 2)
     if y.shape != residual.shape or weight.shape[0] != y.shape[1]:
         raise KernelError("rms_norm_add: y, residual and weight do not fit")
     lib = build.load("elementwise")
-    _check(lib.hk_rms_norm_add(_ptr(y), _ptr(weight), _ptr(residual), y.shape[0], y.shape[1], ctypes.c_float(eps), _stream()),
-           "rms_norm_add")
+    _check(lib.hk_rms_norm_add(_ptr(y), _ptr(weight), _ptr(residual), y.shape[0], y.shape[1], ctypes.c_float(eps), _ptr(narrow),
+                               _stream()), "rms_norm_add")
 
 
 def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:

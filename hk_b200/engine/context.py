@@ -39,6 +39,7 @@ class StepContext:
     fixed_shape: bool = False
     max_context: int = 0
     page_tokens: int = 0        # tokens per cache page (0: not said); a part may cut its work to fit the pages
+    residual_narrow: Optional[torch.Tensor] = None   # the residual stream rounded to the compute type, while a layer keeps it up
 
 
 def table_parts(model: Part) -> List[Tuple[Hashable, Part]]:

@@ -62,8 +62,19 @@ class ModelSpec(Part):
     def forward(self, ctx, caches) -> torch.Tensor:
         """Runs the step's tokens through the schedule; returns the float32 residual [n, hidden]."""
         x = torch.empty((ctx.n_tokens, self.hidden), dtype=torch.float32, device=ctx.token_ids.device)
-        self.embedding.forward(ctx.token_ids, x)
+        # a layer whose sublayers read the residual stream itself wants a copy of it in the compute type; the kernel that
+        # writes the residual writes that copy too (`ctx.residual_narrow`), and a layer that does not keep it up drops it
+        keeps = [getattr(self.layers[call.layer], "keeps_narrow_residual", False) for call in self.schedule]
+        ctx.residual_narrow = None
+        if keeps and keeps[0] and ctx.precision.compute != torch.float32:
+            ctx.residual_narrow = torch.empty((ctx.n_tokens, self.hidden), dtype=ctx.precision.compute, device=x.device)
+        if ctx.residual_narrow is not None:
+            self.embedding.forward(ctx.token_ids, x, ctx.residual_narrow)
+        else:
+            self.embedding.forward(ctx.token_ids, x)
         for ci, call in enumerate(self.schedule):
             own = call.cache_of is None
+            if not keeps[ci]:
+                ctx.residual_narrow = None
             self.layers[call.layer].forward(x, ctx, caches[ci if own else call.cache_of], write_cache=own)
         return x

@@ -1,15 +1,16 @@
 from .attention import GQAAttention
 from .base import (KVCacheSpec, MATRIX, ParamSpec, Part, Precision, StateSpec, StepTables, TABLE, VECTOR, part_class,
                    register_part)
-from .block import PreNormBlock, SandwichNormBlock
+from .block import PostNormBlock, PreNormBlock, SandwichNormBlock
 from .embedding import OutputHead, TokenEmbedding
 from .feed_forward import PolyNormFeedForward, RoutedFeedForward, SwiGLUFeedForward
+from .latent_attention import LatentAttention
 from .norm import RMSNorm
 from .position import RopeScaling, RotaryEmbedding
 from .recurrent import GeneralDeltaRule, MinGRU
 
 __all__ = [
-    "GQAAttention", "GeneralDeltaRule", "KVCacheSpec", "MinGRU", "PolyNormFeedForward", "RoutedFeedForward", "SandwichNormBlock", "MATRIX", "OutputHead", "ParamSpec", "Part", "Precision", "PreNormBlock",
+    "GQAAttention", "GeneralDeltaRule", "KVCacheSpec", "LatentAttention", "MinGRU", "PostNormBlock", "PolyNormFeedForward", "RoutedFeedForward", "SandwichNormBlock", "MATRIX", "OutputHead", "ParamSpec", "Part", "Precision", "PreNormBlock",
     "RMSNorm", "RopeScaling", "RotaryEmbedding", "StateSpec", "StepTables", "SwiGLUFeedForward", "TABLE", "TokenEmbedding", "VECTOR",
     "part_class", "register_part",
 ]

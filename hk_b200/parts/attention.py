@@ -21,8 +21,15 @@ Further parameters, for designs other than the reference's:
   `value_from_key` drops the v projection: a token's value is its key as projected, before rotation and norm,
   of which the first `v_head_dim` dims are kept (the cache then holds both forms of the key);
   `sink` adds a term to the softmax's denominator, a key of score 0 that has no value:
-  p_j = exp(s_j) / (1 + sum exp(s_j));
-  `names` renames the tensors (keys q, k, v, o, q_norm, k_norm, and q_bias, k_bias, v_bias, o_bias).
+  p_j = exp(s_j) / (1 + sum exp(s_j)); with `sink_weights` that score is a number per query head learned with the
+  model (tensor `sink` [H]): p_j = exp(s_j) / (exp(sink_h) + sum exp(s_j));
+  `v_head_dim` without `value_from_key` gives the values a width of their own (W_v is [G * v_head_dim, hidden]);
+  `softcap` c bounds the scores: s <- c tanh(s / c), after the scale and before the softmax;
+  `chunk` s cuts the sequence into blocks of s positions counted from position 0: a token sees the keys of its own
+  block up to itself and none of an earlier block;
+  `gate` multiplies the concatenated heads' outputs, before W_o, element by element with sigmoid(W_g x) of the
+  mixer's own input (tensor `g` [H * v_head_dim, hidden], fused into the q/k/v product);
+  `names` renames the tensors (keys q, k, v, o, q_norm, k_norm, sink, gate, and q_bias, k_bias, v_bias, o_bias).
 """
 from __future__ import annotations
 
@@ -44,7 +51,8 @@ class GQAAttention(Part):
                  window: Optional[int] = None, scale: Optional[float] = None, qkv_bias: bool = False,
                  o_bias: bool = False, qk_norm_after: bool = False, qk_norm_weight: bool = True,
                  value_from_key: bool = False, v_head_dim: Optional[int] = None, sink: bool = False,
-                 names: Optional[Dict[str, str]] = None):
+                 names: Optional[Dict[str, str]] = None, sink_weights: bool = False, softcap: Optional[float] = None,
+                 chunk: Optional[int] = None, gate: bool = False):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
         if head_dim > 256 or head_dim < 2:
@@ -53,12 +61,20 @@ class GQAAttention(Part):
             raise ValueError("the rotary width exceeds head_dim")
         self.hidden, self.H, self.G, self.hd = hidden, n_heads, n_kv_heads, head_dim
         self.vd = head_dim if v_head_dim is None else int(v_head_dim)
-        if not 1 <= self.vd <= head_dim or (self.vd != head_dim and not value_from_key):
-            raise ValueError(f"value size {self.vd} must be head_dim, or at most head_dim when the values are the keys")
+        if not 1 <= self.vd <= 256 or (self.vd > head_dim and value_from_key):
+            raise ValueError(f"value size {self.vd} must be in 1..256, and at most head_dim when the values are the keys")
+        if sink_weights and not sink:
+            raise ValueError("sink_weights needs sink")
+        self.sink_weights, self.gate = bool(sink_weights), bool(gate)
+        self.softcap = float(softcap) if softcap else 0.0
+        self.chunk = int(chunk) if chunk else 0
+        if self.softcap < 0 or self.chunk < 0:
+            raise ValueError("softcap and chunk must be positive (or absent)")
         self.qk_norm_after, self.qk_norm_weight = bool(qk_norm_after), bool(qk_norm_weight)
         self.value_from_key, self.sink = bool(value_from_key), bool(sink)
         self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "q_bias": "q_proj.bias",
+                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sink", "gate": "g_proj.weight",
+                      "q_bias": "q_proj.bias",
                       "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias"}
         self.names.update(names or {})
         self.prefix = prefix
@@ -69,7 +85,7 @@ class GQAAttention(Part):
         # biases on the projections: the reference turns `qkv_bias` on by architecture (src/engine/config.zig:313)
         self.qkv_bias, self.o_bias = bool(qkv_bias), bool(o_bias)
         self.b_qkv = self.b_o = None
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.sinks = None
         self._tables_key = None        # set at bind: the flash kernels' work items, when they take these sizes
         self._sm_count = 0
 
@@ -77,10 +93,16 @@ class GQAAttention(Part):
     def kernel_libraries(self, bfloat16: bool):
         """The flash kernels are compiled only for a model one of whose attention parts can use them."""
         from ..csrc import attention_fast
-        if not bfloat16 or self.vd != self.hd or not attention_fast.supported(self.hd, self.H // self.G):
+        if not bfloat16 or not self._flash_takes():
             return ()
         return ("attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.hd, self.H // self.G) \
             and not self.sink else ("attention_flash",)
+
+    def _flash_takes(self) -> bool:
+        """Whether the flash kernels know everything this mixer asks of the scores."""
+        from ..csrc import attention_fast
+        return self.vd == self.hd and attention_fast.supported(self.hd, self.H // self.G) \
+            and attention_fast.options_supported(self.softcap, self.chunk, self.sink_weights)
 
     def children(self):
         return (self.position,) if self.position is not None else ()
@@ -93,7 +115,11 @@ class GQAAttention(Part):
             p + nm["o"]: ParamSpec((d, H * self.vd), MATRIX),
         }
         if not self.value_from_key:
-            specs[p + nm["v"]] = ParamSpec((G * hd, d), MATRIX)
+            specs[p + nm["v"]] = ParamSpec((G * self.vd, d), MATRIX)
+        if self.sink_weights:
+            specs[p + nm["sink"]] = ParamSpec((H,), VECTOR)
+        if self.gate:
+            specs[p + nm["gate"]] = ParamSpec((H * self.vd, d), MATRIX)
         if self.qk_norm_eps is not None and self.qk_norm_weight:
             specs[p + nm["q_norm"]] = ParamSpec((hd,), VECTOR, "one_plus_normal")
             specs[p + nm["k_norm"]] = ParamSpec((hd,), VECTOR, "one_plus_normal")
@@ -113,6 +139,11 @@ class GQAAttention(Part):
         p, nm = self.prefix, self.names
         parts = "qk" if self.value_from_key else "qkv"
         qkv = [tensors[p + nm[c]] for c in parts]
+        self._qkv_width = sum(int(t.shape[0]) for t in qkv)
+        if self.gate:                        # the gate's logits are further columns of the same product
+            qkv.append(tensors[p + nm["gate"]])
+        if self.sink_weights:
+            self.sinks = tensors[p + nm["sink"]]
         wide = torch.float32 if any(t.dtype == torch.float32 for t in qkv) else qkv[0].dtype    # one kept in 32-bit: all are
         self.w_qkv = torch.cat([t.to(wide) for t in qkv], dim=0).contiguous()
         self.w_o = tensors[p + nm["o"]]
@@ -124,8 +155,8 @@ class GQAAttention(Part):
             self.q_norm = tensors[p + nm["q_norm"]]
             self.k_norm = tensors[p + nm["k_norm"]]
         from ..csrc import attention_fast
-        if precision.compute == torch.bfloat16 and attention_fast.supported(self.hd, self.H // self.G) and self.vd == self.hd:
-            self._tables_key = ("paged_attention_items", self.window or 0, self.H, self.G, self.hd, self.sink)
+        if precision.compute == torch.bfloat16 and self._flash_takes():
+            self._tables_key = ("paged_attention_items", self.window or 0, self.H, self.G, self.hd, self.sink, self.chunk)
             self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
 
     # -- the step's work items (host-built; see parts.base) --------------------------------
@@ -177,8 +208,10 @@ class GQAAttention(Part):
         n = xb.shape[0]
         H, G, hd = self.H, self.G, self.hd
         plan = self._plan(ctx) if xb.dtype == torch.bfloat16 else None
-        qkv = torch.empty((n, self.w_qkv.shape[0]), dtype=torch.float32, device=xb.device)
-        ops.gemm(xb, self.w_qkv, qkv)
+        proj = torch.empty((n, self.w_qkv.shape[0]), dtype=torch.float32, device=xb.device)
+        ops.gemm(xb, self.w_qkv, proj)
+        qkv = proj[:, :self._qkv_width] if self.gate else proj
+        gate = proj[:, self._qkv_width:] if self.gate else None
         q = torch.empty((n, H * hd), dtype=xb.dtype, device=xb.device)
         cos = sin = None
         rot = 0
@@ -195,7 +228,7 @@ class GQAAttention(Part):
         att = torch.empty((n, H * self.vd), dtype=xb.dtype, device=xb.device)
         ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.slot_of_token,
                             att, H, G, hd, cache.page_tokens, self.window or 0, self.scale,
-                            plan=plan, sink=self.sink)
+                            plan=plan, sink=self.sink, sinks=self.sinks, softcap=self.softcap, chunk=self.chunk, gate=gate)
         ops.gemm(att, self.w_o, residual, accumulate=accumulate, bias=self.b_o)
 
 

@@ -69,3 +69,47 @@ class SandwichNormBlock(Part):
 
 
 register_part("block", "sandwich_norm", SandwichNormBlock)
+
+
+class PostNormBlock(Part):
+    """A layer that norms only what its sublayers give back:
+        x <- x + post_mixer_norm(mixer(x));   x <- x + post_ffn_norm(ffn(x))
+    The sublayers read the residual stream itself.  In 32-bit that is the residual tensor; when serving, the
+    bfloat16 copy that the products read is written by the kernel that last changed the residual (the norm + residual
+    sum of the sublayer before, or the embedding) and handed on through `ctx.residual_narrow`.  Without a feed-forward
+    the second half is absent."""
+    graph_safe = True   # reads the batch from device tensors only
+    keeps_narrow_residual = True
+
+    def __init__(self, mixer, post_mixer_norm, feed_forward=None, post_ffn_norm=None):
+        if (feed_forward is None) != (post_ffn_norm is None):
+            raise ValueError("a feed-forward comes with its norm, or neither is given")
+        self.mixer, self.post_mixer_norm = mixer, post_mixer_norm
+        self.feed_forward, self.post_ffn_norm = feed_forward, post_ffn_norm
+
+    def children(self):
+        return tuple(p for p in (self.mixer, self.post_mixer_norm, self.feed_forward, self.post_ffn_norm) if p is not None)
+
+    def cache_specs(self):
+        return [self.mixer.cache_spec()]
+
+    def forward(self, residual: torch.Tensor, ctx, caches, write_cache: bool = True) -> None:
+        from ..csrc import ops
+        narrow = ctx.precision.compute != torch.float32
+        if not narrow:
+            xb = residual                       # the sublayers read it and write elsewhere
+        else:
+            xb = getattr(ctx, "residual_narrow", None)
+            if xb is None:                      # whoever changed the residual last left no copy
+                xb = torch.empty(residual.shape, dtype=ctx.precision.compute, device=residual.device)
+                xb.copy_(residual)
+        y = torch.empty_like(residual)
+        self.mixer.forward(xb, y, ctx, caches[0], write_cache, accumulate=False)
+        ops.rms_norm_add(y, self.post_mixer_norm.weight, self.post_mixer_norm.eps, residual, xb if narrow else None)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(xb, y, ctx, accumulate=False)
+            ops.rms_norm_add(y, self.post_ffn_norm.weight, self.post_ffn_norm.eps, residual, xb if narrow else None)
+        ctx.residual_narrow = xb if narrow else None
+
+
+register_part("block", "post_norm", PostNormBlock)

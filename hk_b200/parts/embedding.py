@@ -1,7 +1,7 @@
 """Token embedding and output head.
 
 Embedding: x[t, :] = E[token_t, :] widened to the float32 residual
-(src/engine/cpu_backend.zig:237-244).  Head: final norm on the wanted rows only, then
+(src/engine/cpu_backend.zig:237-244), times `scale` (1 unless a design multiplies its embeddings).  Head: final norm on the wanted rows only, then
 logits = xb W_out^T in float32 (cpu_backend.zig:329-357); W_out is `lm_head.weight` when
 the file has it, else the embedding table when the configuration ties them
 (src/engine/weights.zig:124-129; src/convert/hf.zig:313,481-484)."""
@@ -18,8 +18,8 @@ from .base import MATRIX, ParamSpec, Part, Precision
 class TokenEmbedding(Part):
     graph_safe = True   # reads the batch from device tensors only
 
-    def __init__(self, vocab: int, hidden: int, name: str):
-        self.vocab, self.hidden, self.name = vocab, hidden, name
+    def __init__(self, vocab: int, hidden: int, name: str, scale: float = 1.0):
+        self.vocab, self.hidden, self.name, self.scale = vocab, hidden, name, float(scale)
         self.table = None
 
     def own_param_specs(self) -> Dict[str, ParamSpec]:
@@ -28,8 +28,10 @@ class TokenEmbedding(Part):
     def own_bind(self, tensors, precision: Precision) -> None:
         self.table = tensors[self.name]
 
-    def forward(self, token_ids: torch.Tensor, out: torch.Tensor) -> None:
-        ops.embedding(self.table, token_ids, out)
+    def forward(self, token_ids: torch.Tensor, out: torch.Tensor, narrow: Optional[torch.Tensor] = None) -> None:
+        """`narrow` (bfloat16, out's shape): also receives the rows rounded, for a first layer that reads the residual
+        stream itself."""
+        ops.embedding(self.table, token_ids, out, self.scale, narrow)
 
 
 class OutputHead(Part):

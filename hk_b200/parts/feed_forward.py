@@ -1,7 +1,8 @@
 """SwiGLU feed-forward: residual += (silu(xb Wg^T) * (xb Wu^T)) Wd^T, no biases
 (src/engine/cpu_backend.zig:308-323, src/engine/ops.zig:65-80).  Gate and up are one
 product over the concatenated weight [2F, d] (the reference fuses them into one parallel
-region: src/engine/matmul.zig:93-96)."""
+region: src/engine/matmul.zig:93-96).  The gate's activation is a parameter (`act`: silu, or gelu_tanh =
+0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), which makes it a GeGLU), and so are the tensors' names."""
 from __future__ import annotations
 
 from typing import Dict
@@ -15,32 +16,36 @@ from .base import MATRIX, VECTOR, ParamSpec, Part, Precision, register_part
 class SwiGLUFeedForward(Part):
     graph_safe = True   # reads the batch from device tensors only
 
-    def __init__(self, hidden: int, intermediate: int, prefix: str):
-        self.hidden, self.F, self.prefix = hidden, intermediate, prefix
+    def __init__(self, hidden: int, intermediate: int, prefix: str, act: str = "silu", names=None):
+        if act not in ops.GLU_ACTS:
+            raise ValueError(f"activation '{act}' is not one of {', '.join(ops.GLU_ACTS)}")
+        self.hidden, self.F, self.prefix, self.act = hidden, intermediate, prefix, act
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(names or {})
         self.w_gate_up = self.w_down = None
 
     def own_param_specs(self) -> Dict[str, ParamSpec]:
-        p = self.prefix
+        p, nm = self.prefix, self.names
         return {
-            p + "gate_proj.weight": ParamSpec((self.F, self.hidden), MATRIX),
-            p + "up_proj.weight": ParamSpec((self.F, self.hidden), MATRIX),
-            p + "down_proj.weight": ParamSpec((self.hidden, self.F), MATRIX),
+            p + nm["gate"]: ParamSpec((self.F, self.hidden), MATRIX),
+            p + nm["up"]: ParamSpec((self.F, self.hidden), MATRIX),
+            p + nm["down"]: ParamSpec((self.hidden, self.F), MATRIX),
         }
 
     def own_bind(self, tensors, precision: Precision) -> None:
-        p = self.prefix
-        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        p, nm = self.prefix, self.names
+        gate, up = tensors[p + nm["gate"]], tensors[p + nm["up"]]
         # One matrix [all gate rows | all up rows]: one product gives both halves, and the tensor-core kernels take a
         # tile's rows half from each so that SwiGLU runs in their epilogue (cf. the reference's fused gate/up product,
         # shaders/swiglu_pair.comp:2).
         if gate.dtype != up.dtype:                  # one of them kept in 32-bit: both are
             gate, up = gate.float(), up.float()
         self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
-        self.w_down = tensors[p + "down_proj.weight"]
+        self.w_down = tensors[p + nm["down"]]
 
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, accumulate: bool = True) -> None:
         h = torch.empty((xb.shape[0], self.F), dtype=xb.dtype, device=xb.device)
-        ops.gemm_swiglu(xb, self.w_gate_up, h)
+        ops.gemm_swiglu(xb, self.w_gate_up, h, self.act)
         ops.gemm(h, self.w_down, residual, accumulate=accumulate)
 
 

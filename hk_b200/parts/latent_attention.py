@@ -1,0 +1,110 @@
+"""Attention over a compressed cache ("latent attention"), as a mixer part.
+
+Per token the mixer keeps ONE vector of `kv_rank + rot_dim` numbers instead of keys and values for every head:
+    q = W_q x                      per head [plain_dim plain | rot_dim rotated by position]
+    W_dkv x                        kv_rank + rot_dim numbers: the first kv_rank, RMS-normed with a weight, are the
+                                   latent c; the last rot_dim, rotated by position, are a key part all heads share
+    head h:  key = [W_uk,h c | shared rotated part],  value = W_uv,h c
+    score = scale * (q_plain . W_uk,h c + q_rot . k_rot),  causal softmax,  y = W_o (concat_h(sum_j p_j W_uv,h c_j) [* sigmoid(W_g x)])
+Nothing but c and the rotated part is cached, and the per-head keys and values are never formed: because the score
+is linear in c, the query is carried into the latent space instead (q_lat,h = W_uk,h^T q_plain,h, one small product
+per head), the attention runs as H query heads over one shared key/value head whose key is the cache row
+[c | k_rot] and whose value is the row's first kv_rank dims, and W_uv,h is applied to the attention's result
+(sum_j p_j c_j).  A decode step therefore reads kv_rank + rot_dim numbers per cached token, whatever the number of
+heads.  Sizes, the norm's eps, the position encoding (its pairing, scaling and magnitude), the scale, a window and
+the output gate are parameters; `names` renames the tensors (keys q, dkv, dkv_norm, uk, uv, gate, o).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import ops
+from .base import KVCacheSpec, MATRIX, VECTOR, ParamSpec, Part, Precision, register_part
+from .position import RotaryEmbedding
+
+
+class LatentAttention(Part):
+    graph_safe = True   # reads the batch from device tensors only
+
+    def __init__(self, hidden: int, n_heads: int, plain_dim: int, rot_dim: int, v_head_dim: int, kv_rank: int, prefix: str,
+                 norm_eps: float, scale: float, position: Optional[RotaryEmbedding] = None, gate: bool = False,
+                 window: Optional[int] = None, names: Optional[Dict[str, str]] = None):
+        if min(n_heads, plain_dim, v_head_dim, kv_rank) < 1 or rot_dim < 0:
+            raise ValueError("heads, plain_dim, v_head_dim and kv_rank must be positive, rot_dim not negative")
+        if kv_rank + rot_dim > 640:
+            raise ValueError(f"a cache row of {kv_rank + rot_dim} numbers is above 640")
+        if position is not None and position.rotary_dim > rot_dim:
+            raise ValueError("the rotary width exceeds rot_dim")
+        self.hidden, self.H, self.dn, self.dr, self.vd, self.r = hidden, n_heads, plain_dim, rot_dim, v_head_dim, kv_rank
+        self.prefix, self.norm_eps, self.scale = prefix, float(norm_eps), float(scale)
+        self.position, self.gate, self.window = position, bool(gate), window
+        self.names = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "gate": "g", "o": "o"}
+        self.names.update(names or {})
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.c_norm = None
+
+    def children(self):
+        return (self.position,) if self.position is not None else ()
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        p, nm, H, d = self.prefix, self.names, self.H, self.hidden
+        specs = {
+            p + nm["q"]: ParamSpec((H * (self.dn + self.dr), d), MATRIX),
+            p + nm["dkv"]: ParamSpec((self.r + self.dr, d), MATRIX),
+            p + nm["dkv_norm"]: ParamSpec((self.r,), VECTOR, "one_plus_normal"),
+            p + nm["uk"]: ParamSpec((H * self.dn, self.r), MATRIX),
+            p + nm["uv"]: ParamSpec((H * self.vd, self.r), MATRIX),
+            p + nm["o"]: ParamSpec((d, H * self.vd), MATRIX),
+        }
+        if self.gate:
+            specs[p + nm["gate"]] = ParamSpec((H * self.vd, d), MATRIX)
+        return specs
+
+    def cache_spec(self):
+        """One shared head whose row is [latent | rotated key part]; no value tensor."""
+        return KVCacheSpec(1, self.r + self.dr, self.window, 0)
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        p, nm, H = self.prefix, self.names, self.H
+        mats = [tensors[p + nm["q"]], tensors[p + nm["dkv"]]] + ([tensors[p + nm["gate"]]] if self.gate else [])
+        wide = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        self.w_in = torch.cat([t.to(wide) for t in mats], dim=0).contiguous()       # one product: q, compressed row, gate
+        dt = precision.compute
+        # q_lat,h = W_uk,h^T q_plain,h: as a product with weights [out = kv_rank, in = plain_dim] per head
+        self.w_uk_t = tensors[p + nm["uk"]].to(dt).view(H, self.dn, self.r).transpose(1, 2).contiguous()
+        self.w_uv = tensors[p + nm["uv"]].to(dt).view(H, self.vd, self.r).contiguous()
+        self.w_o = tensors[p + nm["o"]]
+        self.c_norm = tensors[p + nm["dkv_norm"]]
+
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
+                accumulate: bool = True) -> None:
+        n, dev, dt = xb.shape[0], xb.device, xb.dtype
+        H, dn, dr, r, vd = self.H, self.dn, self.dr, self.r, self.vd
+        proj = torch.empty((n, self.w_in.shape[0]), dtype=torch.float32, device=dev)
+        ops.gemm(xb, self.w_in, proj)
+        q_plain = torch.empty((n, H * dn), dtype=dt, device=dev)
+        q_full = torch.empty((n, H * (r + dr)), dtype=dt, device=dev)
+        cos = sin = None
+        rot, pairing = 0, "half"
+        if self.position is not None:
+            cos, sin, rot = self.position.tables()
+            pairing = self.position.pairing
+        ops.latent_prep(proj, q_plain, q_full, self.c_norm, self.norm_eps, cos, sin, rot, pairing, ctx.positions,
+                        ctx.slot_of_token, cache.block_table, cache.k_pages, H, dn, dr, r, cache.page_tokens,
+                        write_kv=write_cache)
+        ops.gemm_heads(q_plain.view(n, H, dn), self.w_uk_t, q_full.view(n, H, r + dr)[:, :, :r], H)
+        lat = torch.empty((n, H * r), dtype=dt, device=dev)
+        ops.paged_attention(q_full, cache.k_pages, None, cache.block_table, ctx.positions, ctx.slot_of_token, lat,
+                            H, 1, r + dr, cache.page_tokens, self.window or 0, self.scale)
+        att = torch.empty((n, H * vd), dtype=dt, device=dev)
+        if self.gate:
+            o = torch.empty((n, H * vd), dtype=torch.float32, device=dev)
+            ops.gemm_heads(lat.view(n, H, r), self.w_uv, o.view(n, H, vd), H)
+            ops.sigmoid_gate(o, proj[:, H * (dn + dr) + r + dr:], att)
+        else:
+            ops.gemm_heads(lat.view(n, H, r), self.w_uv, att.view(n, H, vd), H)
+        ops.gemm(att, self.w_o, residual, accumulate=accumulate)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

@@ -1,6 +1,7 @@
 """RMS norm: out = x * rsqrt(mean(x^2) + eps) * weight, in float32
 (src/engine/ops.zig:10-29).  Width, eps, the tensor name and an offset added to the stored weight
-(0 here; 1 for checkpoints that store weight - 1) are parameters."""
+(0 here; 1 for checkpoints that store weight - 1) are parameters, and so is a factor on the weight (1 here; a design
+that multiplies what follows the norm by a constant, its logits for instance, has the norm carry that constant)."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -14,11 +15,12 @@ from .base import VECTOR, ParamSpec, Part, Precision, register_part
 class RMSNorm(Part):
     graph_safe = True   # reads the batch from device tensors only
 
-    def __init__(self, width: int, eps: float, weight_name: str, weight_offset: float = 0.0):
+    def __init__(self, width: int, eps: float, weight_name: str, weight_offset: float = 0.0, weight_scale: float = 1.0):
         self.width = width
         self.eps = float(eps)
         self.weight_name = weight_name
         self.weight_offset = float(weight_offset)
+        self.weight_scale = float(weight_scale)
         self.weight: Optional[torch.Tensor] = None
 
     def own_param_specs(self) -> Dict[str, ParamSpec]:
@@ -28,6 +30,8 @@ class RMSNorm(Part):
         self.weight = tensors[self.weight_name]
         if self.weight_offset != 0.0:
             self.weight = (self.weight + self.weight_offset).contiguous()     # folded in once; the kernel is the same
+        if self.weight_scale != 1.0:
+            self.weight = (self.weight * self.weight_scale).contiguous()
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
         ops.rms_norm(x, self.weight, self.eps, out, rows)

@@ -84,8 +84,6 @@ class RotaryEmbedding(Part):
                 return n * math.log(r.orig_ctx / (rotations * 2.0 * math.pi)) / (2.0 * math.log(self.theta))
             low = max(0.0, math.floor(corr(r.beta_fast)))
             high = min(n - 1.0, math.ceil(corr(r.beta_slow)))
-            if low == high:
-                high += 0.001
         out = []
         for i in range(n // 2):
             inv = math.pow(self.theta, -(2.0 * i) / n)
@@ -101,7 +99,7 @@ class RotaryEmbedding(Part):
                     smooth = (r.orig_ctx / wavelen - r.low_freq_factor) / (r.high_freq_factor - r.low_freq_factor)
                     v = (1.0 - smooth) * inv / r.factor + smooth * inv
             elif r.kind == "yarn":
-                ramp = min(1.0, max(0.0, (i - low) / (high - low)))
+                ramp = min(1.0, max(0.0, (i - low) / max(high - low, 0.001)))
                 keep = 1.0 - ramp          # high-frequency dims (ramp 0) keep the original frequency
                 v = (inv / r.factor) * (1.0 - keep) + inv * keep
             else:
