@@ -43,8 +43,14 @@ def supported(hd: int, group: int) -> bool:
 
 def options_supported(softcap: float, chunk: int, sink_weights: bool) -> bool:
     """Whether the flash kernels know these options of the scores (a bound on the scores, a block-wise mask, a learned
-    score for the sink): not yet, such a mixer takes the generic kernel."""
-    return not (softcap or chunk or sink_weights)
+    score for the sink): the mma.sync prompt kernel and both decode kernels do; the tcgen05 prompt kernels do not, and
+    a mixer that uses any of them (or a sink) is not given those (`plain_scores`)."""
+    return True
+
+
+def plain_scores(sink: bool, softcap: float, chunk: int) -> bool:
+    """Scores that the tcgen05 prompt kernels compute: scale, causality and a window, nothing else."""
+    return not (sink or softcap or chunk)
 
 
 def tc_prefill_supported(hd: int, group: int) -> bool:
@@ -82,13 +88,15 @@ def decode_splits(n_rows: int, n_kv_heads: int, sm_count: int) -> int:
 
 
 def plan_arrays(slots, q_starts, q_lens, start_positions, n_tokens: int, window: int, H: int, G: int,
-                sm_count: int, fixed_splits: int = 0, max_context: int = 0, prefill_rows: int = 64):
+                sm_count: int, fixed_splits: int = 0, max_context: int = 0, prefill_rows: int = 64, chunk: int = 0):
     """The plan on the host: (items int32 [n_items, 8], merge int32 [3, n_tokens] or None, PlanInfo), or None
     when the kernels do not take this grouping.  `fixed_splits` > 0 forces that many items per run (a shape
     that does not change from step to step, for captured decode graphs); `max_context` then bounds the key
     range any later step can bring, which sizes the kernel's page-id buffer.  `prefill_rows`: rows per CTA for
     batches with prompt portions: 64 (the mma.sync kernel), 128 (the tcgen05 kernel, head sizes 64 and 128) or 256
-    (its variant with two query tiles per CTA, which also wants TMA-able pages: `tc2_prefill_supported`)."""
+    (its variant with two query tiles per CTA, which also wants TMA-able pages: `tc2_prefill_supported`).
+    `chunk` > 0: a token sees no key before the start of its own block of `chunk` positions, so an item's keys begin
+    at the block start of its first token (the kernel masks row by row where an item crosses a block's edge)."""
     group = H // G
     nw = 1 if all(l == 1 for l in q_lens) else prefill_rows // 16
     rows = 16 * nw
@@ -98,7 +106,7 @@ def plan_arrays(slots, q_starts, q_lens, start_positions, n_tokens: int, window:
         nw, rows = 4, 64
     tpb = rows // group
     if fixed_splits > 0 and nw == 1:
-        return _decode_plan(slots, q_starts, start_positions, n_tokens, window, fixed_splits, max_context)
+        return _decode_plan(slots, q_starts, start_positions, n_tokens, window, fixed_splits, max_context, chunk)
     runs = []
     for slot, qs, ql, p0 in zip(slots, q_starts, q_lens, start_positions):
         for b0 in range(0, ql, tpb):
@@ -106,6 +114,8 @@ def plan_arrays(slots, q_starts, q_lens, start_positions, n_tokens: int, window:
             pos0 = p0 + b0
             kv_hi = pos0 + n
             kv_lo = max(0, pos0 - window + 1) if window > 0 else 0
+            if chunk > 0:
+                kv_lo = max(kv_lo, (pos0 // chunk) * chunk)
             runs.append((qs + b0, n, slot, pos0, kv_lo, kv_hi))
     if nw != 1:
         # longest key ranges first: the heavy items of a causal prompt (its last rows) must not form the tail
@@ -144,7 +154,7 @@ def plan_arrays(slots, q_starts, q_lens, start_positions, n_tokens: int, window:
     return items, (merge if n_parts else None), PlanInfo(nw, len(recs), n_parts, max_keys)
 
 
-def _decode_plan(slots, q_starts, start_positions, n_tokens, window, splits, max_context):
+def _decode_plan(slots, q_starts, start_positions, n_tokens, window, splits, max_context, chunk=0):
     """The plan of a batch of single tokens with a fixed number of key splits, in array arithmetic (this runs
     on the host before every replayed decode step).  Same items as the general loop gives."""
     B = len(slots)
@@ -153,6 +163,8 @@ def _decode_plan(slots, q_starts, start_positions, n_tokens, window, splits, max
     qrow = np.asarray(q_starts, dtype=np.int64)
     kv_hi = pos + 1
     kv_lo = np.maximum(0, pos - window + 1) if window > 0 else np.zeros(B, dtype=np.int64)
+    if chunk > 0:
+        kv_lo = np.maximum(kv_lo, (pos // chunk) * chunk)
     kv_len = kv_hi - kv_lo
     max_keys = int(kv_len.max()) if B else 0
     if max_context > 0:
@@ -187,10 +199,10 @@ def plan_on_device(info: PlanInfo, items: torch.Tensor, merge: Optional[torch.Te
 
 def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: int, H: int, G: int,
                sm_count: int, upload: Callable[[np.ndarray], torch.Tensor], fixed_splits: int = 0,
-               max_context: int = 0, prefill_rows: int = 64) -> Optional[FlashPlan]:
+               max_context: int = 0, prefill_rows: int = 64, chunk: int = 0) -> Optional[FlashPlan]:
     """`plan_arrays` followed by `upload(int32 array) -> device tensor` for each array."""
     got = plan_arrays(slots, q_starts, q_lens, start_positions, n_tokens, window, H, G, sm_count, fixed_splits,
-                      max_context, prefill_rows)
+                      max_context, prefill_rows, chunk)
     if got is None:
         return None
     items, merge, info = got
@@ -206,11 +218,13 @@ def tma_decode_supported(hd: int, group: int, page_tokens: int) -> bool:
 
 
 def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan: FlashPlan,
-        allow_tma: bool = True, sink: bool = False) -> bool:
+        allow_tma: bool = True, sink: bool = False, sinks=None, softcap: float = 0.0, chunk: int = 0) -> bool:
     from . import gemm_fast, ops
     if not supported(hd, H // G) or plan is None:
         return False
     sk = 1 if sink else 0
+    plain = plain_scores(sink, softcap, chunk)
+    extra = (_ptr(sinks), ctypes.c_float(softcap), int(chunk))
     lib = build.load("attention_flash")
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     rows = 16 * plan.nw
@@ -219,7 +233,7 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
         part_o = torch.empty((plan.n_parts, G, rows, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((plan.n_parts, G, rows, 2), dtype=torch.float32, device=q.device)
     if plan.nw == 16:
-        if sink or plan.n_parts or not tc2_prefill_supported(hd, H // G, int(page_tokens)):
+        if not plain or plan.n_parts or not tc2_prefill_supported(hd, H // G, int(page_tokens)):
             return False
         lib_tc = build.load("attention_prefill_tc")
         code = lib_tc.hk_attention_prefill_tc2(
@@ -232,7 +246,7 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
         ops._check(code, "paged_attention (tcgen05 prefill, two query tiles)")
         return True
     if plan.nw == 8:
-        if sink or plan.n_parts or not tc_prefill_supported(hd, H // G):
+        if not plain or plan.n_parts or not tc_prefill_supported(hd, H // G):
             return False
         lib_tc = build.load("attention_prefill_tc")
         code = lib_tc.hk_attention_prefill_tc(
@@ -249,17 +263,17 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
             _ptr(q), _ptr(k_pages), _ptr(v_pages), ctypes.c_longlong(k_pages.shape[0]), _ptr(block_table),
             int(block_table.shape[1]), _ptr(plan.items), plan.n_items, _ptr(out), _ptr(part_o), _ptr(part_ml), H, G, hd,
             int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)), sk, plan.max_keys // int(page_tokens) + 2,
-            _ptr(gemm_fast.status_flag(q.device)), stream)
+            _ptr(gemm_fast.status_flag(q.device)), *extra, stream)
     if code == _UNSUPPORTED:
         code = lib.hk_attention_flash(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), int(block_table.shape[1]),
                                       _ptr(plan.items), plan.n_items, plan.nw, _ptr(out), _ptr(part_o), _ptr(part_ml), H, G, hd,
                                       int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)), sk,
-                                      plan.max_keys // int(page_tokens) + 2, stream)
+                                      plan.max_keys // int(page_tokens) + 2, *extra, stream)
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "paged_attention (flash)")
     if plan.n_parts:
         code = lib.hk_attention_combine(_ptr(part_o), _ptr(part_ml), _ptr(plan.first), _ptr(plan.count), _ptr(plan.row0),
-                                        _ptr(out), q.shape[0], H, G, hd, rows, sk, stream)
+                                        _ptr(out), q.shape[0], H, G, hd, rows, sk, _ptr(sinks), stream)
         ops._check(code, "paged_attention (combine)")
     return True

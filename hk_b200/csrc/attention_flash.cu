@@ -36,6 +36,30 @@ struct Item {
   int pad;
 };
 
+// What a mixer may ask of the scores beyond scale, window and causality; everything off at zero / null.
+struct ScoreOpts {
+  int sink;             // 1: one more term in the softmax's denominator, a key without a value
+  const float* sinks;   // its score per query head (natural units); null: 0
+  float cap_log2;       // soft cap c on the scores, times log2(e): s <- c tanh(s / c); 0: none
+  float cap_in;         // scale / c
+  int chunk;            // a row at position p sees no key before (p / chunk) * chunk; 0: no such mask
+};
+
+// scale (and cap) a raw dot product into the base-2 exponent domain
+__device__ __forceinline__ float scaled_score(float s, float scale_log2, const ScoreOpts& so) {
+  if (so.cap_log2 > 0.f) {
+    // tanh(x) = 1 - 2 / (e^(2x) + 1): absolute error about 1e-7, which is what counts under the exponential
+    const float t = exp2f(2.8853900817779268f * s * so.cap_in);
+    return so.cap_log2 * (1.0f - __fdividef(2.0f, t + 1.0f));
+  }
+  return s * scale_log2;
+}
+
+// the sink's score in the base-2 domain for query head h
+__device__ __forceinline__ float sink_log2(const ScoreOpts& so, int h) {
+  return so.sinks ? so.sinks[h] * 1.4426950408889634f : 0.f;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -70,7 +94,7 @@ __global__ void __launch_bounds__(NW * 32, 3)
 attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                        const int* __restrict__ block_table, int table_stride, const Item* __restrict__ items,
                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G,
-                       int page_tokens, int window, float scale_log2, int sink) {
+                       int page_tokens, int window, float scale_log2, ScoreOpts so) {
   constexpr int ROWS = NW * 16;
   constexpr int LD = HD + 8;            // padded row: (HD/8 + 1) 16-byte chunks, an odd count -> no ldmatrix conflicts
   constexpr int CPR = HD / 8;           // 16-byte chunks per row
@@ -100,6 +124,7 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
     if (!valid[i]) tq = 0;
     pos[i] = it.pos0 + tq;
     lo[i] = window > 0 ? max(0, pos[i] - window + 1) : 0;
+    if (so.chunk > 0) lo[i] = max(lo[i], (pos[i] / so.chunk) * so.chunk);
     qp[i] = q + ((size_t)(it.q_row0 + tq) * H + g * group + row[i] % group) * HD;
   }
 
@@ -189,7 +214,7 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
       for (int n = 0; n < TILE_N / 8; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          s[n][e] *= scale_log2;
+          s[n][e] = scaled_score(s[n][e], scale_log2, so);
           mt[e >> 1] = fmaxf(mt[e >> 1], s[n][e]);
         }
     } else {
@@ -200,7 +225,7 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
           const int i = e >> 1;
           const int j = t * TILE_N + n * 8 + 2 * qt + (e & 1);
           const bool ok = valid[i] && j >= lo[i] && j <= pos[i] && j >= it.kv_lo && j < it.kv_hi;
-          s[n][e] = ok ? s[n][e] * scale_log2 : -CUDART_INF_F;
+          s[n][e] = ok ? scaled_score(s[n][e], scale_log2, so) : -CUDART_INF_F;
           mt[i] = fmaxf(mt[i], s[n][e]);
         }
     }
@@ -263,7 +288,7 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
       const int tq = row[i] / group;
       bf16* op = out + ((size_t)(it.q_row0 + tq) * H + g * group + row[i] % group) * HD;
       // a sink adds exp(0 - max) to the denominator: a key of score 0 that has no value
-      const float lt = l[i] + ((sink && m[i] > -CUDART_INF_F) ? exp2f(-m[i]) : 0.f);
+      const float lt = l[i] + ((so.sink && m[i] > -CUDART_INF_F) ? exp2f(sink_log2(so, g * group + row[i] % group) - m[i]) : 0.f);
       const float inv = lt > 0.f ? 1.0f / lt : 0.f;
 #pragma unroll
       for (int n = 0; n < HD / 8; ++n)
@@ -297,7 +322,7 @@ __global__ void __launch_bounds__(DW * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int table_stride, const Item* __restrict__ items,
                         bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G,
-                        int page_tokens, int window, float scale_log2, int sink, int pages_cap) {
+                        int page_tokens, int window, float scale_log2, ScoreOpts so, int pages_cap) {
   constexpr int ROWS = 16;
   constexpr int LD = HD + 8, CPR = HD / 8, KSTEPS = HD / 16;
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -327,6 +352,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     if (!valid[i]) tq = 0;
     pos[i] = it.pos0 + tq;
     lo[i] = window > 0 ? max(0, pos[i] - window + 1) : 0;
+    if (so.chunk > 0) lo[i] = max(lo[i], (pos[i] / so.chunk) * so.chunk);
     qp[i] = q + ((size_t)(it.q_row0 + tq) * H + g * group + row[i] % group) * HD;
   }
   uint32_t qf[KSTEPS][4];
@@ -400,7 +426,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         const int i = e >> 1;
         const int j = t * DT + warp * 16 + n * 8 + 2 * qt + (e & 1);
         const bool ok = valid[i] && j >= lo[i] && j <= pos[i] && j >= it.kv_lo && j < it.kv_hi;
-        s[n][e] = ok ? s[n][e] * scale_log2 : -CUDART_INF_F;
+        s[n][e] = ok ? scaled_score(s[n][e], scale_log2, so) : -CUDART_INF_F;
         mt[i] = fmaxf(mt[i], s[n][e]);
       }
     float corr[2], msafe[2];
@@ -479,7 +505,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     }
     if (it.part < 0) {
       const int tq = r / group;
-      if (sink && mx > -CUDART_INF_F) lsum += exp2f(-mx);
+      if (so.sink && mx > -CUDART_INF_F) lsum += exp2f(sink_log2(so, g * group + r % group) - mx);
       if (tq < it.n_tokens)
         out[((size_t)(it.q_row0 + tq) * H + g * group + r % group) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
     } else {
@@ -543,7 +569,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const bf16* __restrict__ q, const int* __restrict__ block_table, int table_stride,
                             const Item* __restrict__ items, bf16* __restrict__ out, float* __restrict__ part_o,
                             float* __restrict__ part_ml, int H, int G, int page_tokens, int box_rows, int window,
-                            float scale_log2, int sink, int pages_cap, int* __restrict__ status) {
+                            float scale_log2, ScoreOpts so, int pages_cap, int* __restrict__ status) {
   constexpr int ROWS = 16;
   constexpr int KSTEPS = HD / 16;
   constexpr int TILE_BYTES = TT * HD * 2;            // K (or V) of one stage
@@ -628,6 +654,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       if (!valid[i]) tq = 0;
       pos[i] = it.pos0 + tq;
       lo[i] = window > 0 ? max(0, pos[i] - window + 1) : 0;
+    if (so.chunk > 0) lo[i] = max(lo[i], (pos[i] / so.chunk) * so.chunk);
       qp[i] = q + ((size_t)(it.q_row0 + tq) * H + g * group + row[i] % group) * HD;
     }
     uint32_t qf[KSTEPS][4];
@@ -680,7 +707,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           const int i = e >> 1;
           const int j = t * TT + warp * 16 + nn * 8 + 2 * qt + (e & 1);
           const bool ok = valid[i] && j >= lo[i] && j <= pos[i] && j >= it.kv_lo && j < it.kv_hi;
-          s[nn][e] = ok ? s[nn][e] * scale_log2 : -CUDART_INF_F;
+          s[nn][e] = ok ? scaled_score(s[nn][e], scale_log2, so) : -CUDART_INF_F;
           mt[i] = fmaxf(mt[i], s[nn][e]);
         }
       float corr[2], msafe[2];
@@ -772,7 +799,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
     if (it.part < 0) {
       const int tq = r / group;
-      if (sink && mx > -CUDART_INF_F) lsum += exp2f(-mx);
+      if (so.sink && mx > -CUDART_INF_F) lsum += exp2f(sink_log2(so, g * group + r % group) - mx);
       if (tq < it.n_tokens)
         out[((size_t)(it.q_row0 + tq) * H + g * group + r % group) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
     } else {
@@ -790,7 +817,7 @@ template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const int* __restrict__ first, const int* __restrict__ count,
                                          const int* __restrict__ row0, bf16* __restrict__ out, int n_tokens, int H, int G,
-                                         int rows, int sink) {
+                                         int rows, ScoreOpts so) {
   pdl_launch_dependents();
   pdl_wait();
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -836,7 +863,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     }
   }
   lsum = warp_sum(lsum);
-  if (sink && mm > -CUDART_INF_F) lsum += exp2f(-mm);
+  if (so.sink && mm > -CUDART_INF_F) lsum += exp2f(sink_log2(so, h) - mm);
   const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
   bf16* op = out + ((size_t)t * H + h) * HD;
 #pragma unroll
@@ -848,20 +875,20 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 
 template <int HD, int NW>
 int launch_flash(const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
-                 void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int sink, cudaStream_t s) {
+                 void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, ScoreOpts so, cudaStream_t s) {
   const size_t smem = (size_t)4 * TILE_N * (HD + 8) * sizeof(bf16) + 2 * TILE_N * sizeof(int);
   static HkSmemCache allowed = {};
   if (int e = hk_allow_smem(attention_flash_kernel<HD, NW>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items * (unsigned)G);
   attention_flash_kernel<HD, NW><<<grid, NW * 32, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                             (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, window,
-                                                            scale_log2, sink);
+                                                            scale_log2, so);
   return hk_launch_status();
 }
 
 template <int HD>
 int launch_decode(const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
-                  void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int sink, int pages_cap,
+                  void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, ScoreOpts so, int pages_cap,
                   cudaStream_t s) {
   const size_t tiles = (size_t)2 * DS * DT * (HD + 8) * sizeof(bf16);
   const size_t merge = (size_t)DW * 16 * (HD + 2) * sizeof(float);
@@ -872,17 +899,26 @@ int launch_decode(const void* q, const void* kp, const void* vp, const int* bt, 
   dim3 grid((unsigned)n_items, (unsigned)G);
   attention_decode_kernel<HD><<<grid, DW * 32, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                          (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, window,
-                                                         scale_log2, sink, pages_cap);
+                                                         scale_log2, so, pages_cap);
   return hk_launch_status();
 }
 
 template <int HD>
 int launch_hd(int nw, const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
-              void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int sink, int pages_cap,
+              void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, ScoreOpts so, int pages_cap,
               cudaStream_t s) {
-  if (nw == 1) return launch_decode<HD>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, sink, pages_cap, s);
-  if (nw == 4) return launch_flash<HD, 4>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, sink, s);
+  if (nw == 1) return launch_decode<HD>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, so, pages_cap, s);
+  if (nw == 4) return launch_flash<HD, 4>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, so, s);
   return HK_ERR_UNSUPPORTED;
+}
+
+ScoreOpts make_opts(int sink, const float* sinks, float softcap, float scale_log2, int chunk) {
+  ScoreOpts so = {sink, sink ? sinks : nullptr, 0.f, 0.f, chunk > 0 ? chunk : 0};
+  if (softcap > 0.f) {
+    so.cap_log2 = softcap * 1.4426950408889634f;
+    so.cap_in = scale_log2 / so.cap_log2;       // scale / softcap
+  }
+  return so;
 }
 
 }  // namespace
@@ -891,29 +927,33 @@ int launch_hd(int nw, const void* q, const void* kp, const void* vp, const int* 
 // nw = 1: the decode variant, 16 rows per CTA whose four warps split the keys.  An item holds at most
 // (16 * nw) / (H / G) query tokens.  part_o [parts, G, 16*nw, hd] and part_ml [parts, G, 16*nw, 2] are
 // fp32 scratch for items with part >= 0.  scale_log2 = scale * log2(e).  pages_cap: the most pages any item's key
-// range spans (the decode variant keeps that many page ids in shared memory).
+// range spans (the decode variant keeps that many page ids in shared memory).  sink, sinks, softcap, chunk: see
+// `ScoreOpts` (sinks: one score per query head or null; softcap and chunk 0 for none).
 HK_API int hk_attention_flash(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                               int table_stride, const void* items, int n_items, int nw, void* out, float* part_o,
                               float* part_ml, int H, int G, int hd, int page_tokens, int window, float scale_log2, int sink,
-                              int pages_cap, void* stream) {
+                              int pages_cap, const float* sinks, float softcap, int chunk, void* stream) {
   if (n_items <= 0) return 0;
+  const ScoreOpts so = make_opts(sink, sinks, softcap, scale_log2, chunk);
   if (G < 1 || H % G != 0 || (H / G) > 16 * nw || G > 65535) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
 #define HK_HD(D) \
-  if (hd == D) return launch_hd<D>(nw, q, k_pages, v_pages, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens, window, scale_log2, sink, pages_cap, s);
+  if (hd == D) return launch_hd<D>(nw, q, k_pages, v_pages, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens, window, scale_log2, so, pages_cap, s);
   HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
 #undef HK_HD
   return HK_ERR_UNSUPPORTED;
 }
 
 HK_API int hk_attention_combine(const float* part_o, const float* part_ml, const int* first, const int* count,
-                                const int* row0, void* out, int n_tokens, int H, int G, int hd, int rows, int sink, void* stream) {
+                                const int* row0, void* out, int n_tokens, int H, int G, int hd, int rows, int sink, const float* sinks,
+                                void* stream) {
   if (n_tokens <= 0) return 0;
+  const ScoreOpts so = make_opts(sink, sinks, 0.f, 0.f, 0);
   cudaStream_t s = (cudaStream_t)stream;
   const int warps = 4;
   const unsigned grid = (unsigned)(((long long)n_tokens * H + warps - 1) / warps);
 #define HK_HD(D) \
-  if (hd == D) return hk_launch(attention_combine_kernel<D>, dim3(grid), dim3(warps * 32), 0, s, part_o, part_ml, first, count, row0, (bf16*)out, n_tokens, H, G, rows, sink);
+  if (hd == D) return hk_launch(attention_combine_kernel<D>, dim3(grid), dim3(warps * 32), 0, s, part_o, part_ml, first, count, row0, (bf16*)out, n_tokens, H, G, rows, so);
   HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
 #undef HK_HD
   return HK_ERR_UNSUPPORTED;
@@ -955,14 +995,14 @@ bool make_page_map(CUtensorMap* map, const void* ptr, unsigned long long rows, i
 template <int HD>
 int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int* bt, int stride, const void* items,
                       int n_items, void* out, float* part_o, float* part_ml, int H, int G, int pt, int box_rows, int window,
-                      float scale_log2, int sink, int pages_cap, int* status, cudaStream_t s) {
+                      float scale_log2, ScoreOpts so, int pages_cap, int* status, cudaStream_t s) {
   const size_t smem = 1024 + (size_t)2 * TS * TT * HD * 2 + 2 * TS * sizeof(uint64_t) + 8 + (size_t)pages_cap * sizeof(int);
   if (smem > 110 * 1024) return HK_ERR_UNSUPPORTED;
   static HkSmemCache allowed = {};
   if (int e = hk_allow_smem(attention_decode_tma_kernel<HD>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items, (unsigned)G);
   return hk_launch_pdl(attention_decode_tma_kernel<HD>, grid, dim3((TW + 1) * 32), smem, s, mk, mv, (const bf16*)q, bt, stride,
-                       (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, box_rows, window, scale_log2, sink, pages_cap, status);
+                       (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, box_rows, window, scale_log2, so, pages_cap, status);
 }
 
 }  // namespace
@@ -973,7 +1013,7 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
 HK_API int hk_attention_decode_tma(const void* q, const void* k_pages, const void* v_pages, long long num_pages,
                                    const int* block_table, int table_stride, const void* items, int n_items, void* out,
                                    float* part_o, float* part_ml, int H, int G, int hd, int page_tokens, int window,
-                                   float scale_log2, int sink, int pages_cap, int* status, void* stream) {
+                                   float scale_log2, ScoreOpts so, int pages_cap, int* status, void* stream) {
   if (n_items <= 0) return 0;
   if (G < 1 || H % G != 0 || (H / G) > 16 || G > 65535) return HK_ERR_UNSUPPORTED;
   if ((hd != 64 && hd != 128) || page_tokens < 16 || (page_tokens & (page_tokens - 1))) return HK_ERR_UNSUPPORTED;
@@ -985,9 +1025,9 @@ HK_API int hk_attention_decode_tma(const void* q, const void* k_pages, const voi
   cudaStream_t s = (cudaStream_t)stream;
   if (hd == 64)
     return launch_decode_tma<64>(mk, mv, q, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens,
-                                 box_rows, window, scale_log2, sink, pages_cap, status, s);
+                                 box_rows, window, scale_log2, so, pages_cap, status, s);
   return launch_decode_tma<128>(mk, mv, q, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens,
-                                box_rows, window, scale_log2, sink, pages_cap, status, s);
+                                box_rows, window, scale_log2, so, pages_cap, status, s);
 }
 
 // ---- the entry point that allocates nothing (see attention_noalloc.h) -------------------------------------
@@ -1032,7 +1072,7 @@ HK_API int hk_attention_decode_noalloc(const void* q, const void* k_pages, const
   float* part_o = scratch;
   float* part_ml = scratch + (size_t)n_parts * G * rows * hd;
   int code = hk_attention_flash(q, k_pages, v_pages, block_table, table_stride, items, n_items, 1, out, part_o, part_ml, H, G,
-                                hd, page_tokens, window, scale_log2, 0, pages_cap, stream);
+                                hd, page_tokens, window, scale_log2, 0, pages_cap, nullptr, 0.f, 0, stream);
   if (code != 0 || n_parts == 0) return code;
-  return hk_attention_combine(part_o, part_ml, first, count, row0, out, n_tokens, H, G, hd, (int)rows, 0, stream);
+  return hk_attention_combine(part_o, part_ml, first, count, row0, out, n_tokens, H, G, hd, (int)rows, 0, nullptr, stream);
 }

@@ -365,11 +365,12 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
         if gate.shape[0] != n:
             raise KernelError("paged_attention: one row of gate logits per token")
     choice = _forced["attention"]
-    plain = v_pages is not None and vd == hd and sinks is None and not softcap and not chunk and gate is None
-    if q.dtype == torch.bfloat16 and choice != "generic" and plan is not None and plain:
+    if q.dtype == torch.bfloat16 and choice != "generic" and plan is not None and v_pages is not None and vd == hd:
         from . import attention_fast
         if attention_fast.run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan,
-                              allow_tma=choice != "flash_cp", sink=sink):
+                              allow_tma=choice != "flash_cp", sink=sink, sinks=sinks, softcap=softcap, chunk=chunk):
+            if gate is not None:
+                sigmoid_gate(out, gate, out)
             return
         if choice is not None:
             raise KernelError(f"paged_attention: the '{choice}' kernel refuses head_dim={hd} page_tokens={page_tokens}")

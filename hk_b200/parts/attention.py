@@ -43,6 +43,45 @@ from .base import KVCacheSpec, MATRIX, VECTOR, ParamSpec, Part, Precision, StepT
 from .position import RotaryEmbedding
 
 
+def flash_step_tables(ctx, H: int, G: int, hd: int, window: int, chunk: int, sm_count: int, plain: bool = True):
+    """The flash kernels' work items for one step, as a part's host-built tables.  `plain`: the scores are scale,
+    causality and a window alone, which is what the tcgen05 prompt kernels compute; a mixer that asks more of its
+    scores (a sink, a cap, a mask of blocks) takes the mma.sync flash kernel for prompts."""
+    from ..csrc import attention_fast
+    tc = attention_fast.tc_prefill_supported(hd, H // G) and ops.forced("attention") != "flash_cp" and plain
+    rows = 128 if tc else 64
+    # the kernel with two query tiles per CTA is the faster one per row, but halves the number of work items: it
+    # is taken when its items still fill the SMs (measured on the 8B layer: equal at 1,024 prompt tokens = 128
+    # items, 1.6 times faster at 2,048, 1.3 times slower at 512), where the pages allow it
+    if tc and attention_fast.tc2_prefill_supported(hd, H // G, ctx.page_tokens):
+        group = H // G
+        items = G * sum(-(-(int(q) * group) // 256) for q in ctx.q_lens if int(q) * group > 128)
+        if items * 20 >= sm_count * 17:
+            rows = 256
+    fixed = attention_fast.decode_splits(ctx.n_tokens, G, sm_count) if ctx.fixed_shape else 0
+    got = attention_fast.plan_arrays(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens,
+                                     window, H, G, sm_count, fixed_splits=fixed,
+                                     max_context=ctx.max_context if ctx.fixed_shape else 0,
+                                     prefill_rows=rows, chunk=chunk)
+    if got is None:
+        return None
+    items, merge, info = got
+    arrays = {"items": items}
+    if merge is not None:
+        arrays["merge"] = merge
+    return StepTables(arrays, info)
+
+
+def flash_plan(ctx, key):
+    """The step's plan on the device from the tables named `key`, or None (the generic kernel takes the step)."""
+    got = ctx.tables.get(key) if key is not None else None
+    if got is None or got[1] is None:
+        return None
+    from ..csrc import attention_fast
+    arrays, info = got
+    return attention_fast.plan_on_device(info, arrays["items"], arrays.get("merge"))
+
+
 class GQAAttention(Part):
     graph_safe = True   # reads the batch from device tensors only
 
@@ -96,7 +135,7 @@ class GQAAttention(Part):
         if not bfloat16 or not self._flash_takes():
             return ()
         return ("attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.hd, self.H // self.G) \
-            and not self.sink else ("attention_flash",)
+            and not (self.sink or self.softcap or self.chunk) else ("attention_flash",)
 
     def _flash_takes(self) -> bool:
         """Whether the flash kernels know everything this mixer asks of the scores."""
@@ -156,7 +195,7 @@ class GQAAttention(Part):
             self.k_norm = tensors[p + nm["k_norm"]]
         from ..csrc import attention_fast
         if precision.compute == torch.bfloat16 and self._flash_takes():
-            self._tables_key = ("paged_attention_items", self.window or 0, self.H, self.G, self.hd, self.sink, self.chunk)
+            self._tables_key = ("paged_attention_items", self.window or 0, self.H, self.G, self.hd, self.sink, self.chunk, bool(self.softcap))
             self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
 
     # -- the step's work items (host-built; see parts.base) --------------------------------
@@ -166,39 +205,11 @@ class GQAAttention(Part):
     def step_tables(self, ctx):
         """Cuts the batch into the flash kernels' work items (csrc/attention_fast.py).  In a step whose shape must
         not change (a captured decode graph) every request's keys go to the same number of splits."""
-        from ..csrc import attention_fast
-        H, G, hd = self.H, self.G, self.hd
-        # the tcgen05 prompt kernels have no sink term: a mixer with a sink takes the mma.sync flash kernel for prompts
-        tc = attention_fast.tc_prefill_supported(hd, H // G) and ops.forced("attention") != "flash_cp" and not self.sink
-        rows = 128 if tc else 64
-        # the kernel with two query tiles per CTA is the faster one per row, but halves the number of work items: it
-        # is taken when its items still fill the SMs (measured on the 8B layer: equal at 1,024 prompt tokens = 128
-        # items, 1.6 times faster at 2,048, 1.3 times slower at 512), where the pages allow it
-        if tc and attention_fast.tc2_prefill_supported(hd, H // G, ctx.page_tokens):
-            group = H // G
-            items = G * sum(-(-(int(q) * group) // 256) for q in ctx.q_lens if int(q) * group > 128)
-            if items * 20 >= self._sm_count * 17:
-                rows = 256
-        fixed = attention_fast.decode_splits(ctx.n_tokens, G, self._sm_count) if ctx.fixed_shape else 0
-        got = attention_fast.plan_arrays(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens,
-                                         self.window or 0, H, G, self._sm_count, fixed_splits=fixed,
-                                         max_context=ctx.max_context if ctx.fixed_shape else 0,
-                                         prefill_rows=rows)
-        if got is None:
-            return None
-        items, merge, info = got
-        arrays = {"items": items}
-        if merge is not None:
-            arrays["merge"] = merge
-        return StepTables(arrays, info)
+        return flash_step_tables(ctx, self.H, self.G, self.hd, self.window or 0, self.chunk, self._sm_count,
+                                 plain=not (self.sink or self.softcap or self.chunk))
 
     def _plan(self, ctx):
-        got = ctx.tables.get(self._tables_key) if self._tables_key is not None else None
-        if got is None or got[1] is None:
-            return None                    # no work items: the generic kernel takes the step
-        from ..csrc import attention_fast
-        arrays, info = got
-        return attention_fast.plan_on_device(info, arrays["items"], arrays.get("merge"))
+        return flash_plan(ctx, self._tables_key)
 
     # -- one step ------------------------------------------------------------------------
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,

@@ -43,6 +43,28 @@ class LatentAttention(Part):
         self.names = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "gate": "g", "o": "o"}
         self.names.update(names or {})
         self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.c_norm = None
+        self._tables_key = None        # set at bind: the flash kernels' work items, when they take a row of this size
+        self._sm_count = 0
+
+    def _flash_takes(self) -> bool:
+        """The flash kernels run H query heads over ONE key/value head whose keys and values are both the cache row
+        (the last rot_dim dims of their result are not used), when the row has a head size they know."""
+        from ..csrc import attention_fast
+        return attention_fast.supported(self.r + self.dr, self.H)
+
+    def kernel_libraries(self, bfloat16: bool):
+        from ..csrc import attention_fast
+        if not bfloat16 or not self._flash_takes():
+            return ()
+        return ("attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.r + self.dr, self.H) \
+            else ("attention_flash",)
+
+    def step_tables_key(self):
+        return self._tables_key
+
+    def step_tables(self, ctx):
+        from .attention import flash_step_tables
+        return flash_step_tables(ctx, self.H, 1, self.r + self.dr, self.window or 0, 0, self._sm_count)
 
     def children(self):
         return (self.position,) if self.position is not None else ()
@@ -76,6 +98,9 @@ class LatentAttention(Part):
         self.w_uv = tensors[p + nm["uv"]].to(dt).view(H, self.vd, self.r).contiguous()
         self.w_o = tensors[p + nm["o"]]
         self.c_norm = tensors[p + nm["dkv_norm"]]
+        if precision.compute == torch.bfloat16 and self._flash_takes():
+            self._tables_key = ("paged_attention_items", self.window or 0, self.H, 1, self.r + self.dr, False, 0, False)
+            self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
 
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
                 accumulate: bool = True) -> None:
@@ -94,16 +119,26 @@ class LatentAttention(Part):
                         ctx.slot_of_token, cache.block_table, cache.k_pages, H, dn, dr, r, cache.page_tokens,
                         write_kv=write_cache)
         ops.gemm_heads(q_plain.view(n, H, dn), self.w_uk_t, q_full.view(n, H, r + dr)[:, :, :r], H)
-        lat = torch.empty((n, H * r), dtype=dt, device=dev)
-        ops.paged_attention(q_full, cache.k_pages, None, cache.block_table, ctx.positions, ctx.slot_of_token, lat,
-                            H, 1, r + dr, cache.page_tokens, self.window or 0, self.scale)
+        from .attention import flash_plan
+        plan = flash_plan(ctx, self._tables_key) if dt == torch.bfloat16 and ops.forced("attention") != "generic" else None
+        if plan is not None:
+            # the flash kernels, with the cache rows as keys AND values: the result's first r dims per head are the latent sums
+            wide = torch.empty((n, H * (r + dr)), dtype=dt, device=dev)
+            ops.paged_attention(q_full, cache.k_pages, cache.k_pages, cache.block_table, ctx.positions, ctx.slot_of_token, wide,
+                                H, 1, r + dr, cache.page_tokens, self.window or 0, self.scale, plan=plan)
+            lat = wide.view(n, H, r + dr)[:, :, :r]
+        else:
+            lat = torch.empty((n, H * r), dtype=dt, device=dev)
+            ops.paged_attention(q_full, cache.k_pages, None, cache.block_table, ctx.positions, ctx.slot_of_token, lat,
+                                H, 1, r + dr, cache.page_tokens, self.window or 0, self.scale)
+            lat = lat.view(n, H, r)
         att = torch.empty((n, H * vd), dtype=dt, device=dev)
         if self.gate:
             o = torch.empty((n, H * vd), dtype=torch.float32, device=dev)
-            ops.gemm_heads(lat.view(n, H, r), self.w_uv, o.view(n, H, vd), H)
+            ops.gemm_heads(lat, self.w_uv, o.view(n, H, vd), H)
             ops.sigmoid_gate(o, proj[:, H * (dn + dr) + r + dr:], att)
         else:
-            ops.gemm_heads(lat.view(n, H, r), self.w_uv, att.view(n, H, vd), H)
+            ops.gemm_heads(lat, self.w_uv, att.view(n, H, vd), H)
         ops.gemm(att, self.w_o, residual, accumulate=accumulate)
 
 

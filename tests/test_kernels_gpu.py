@@ -354,10 +354,10 @@ def test_kernels_refuse_what_they_cannot_do():
         o.embedding(torch.zeros(4, 8), torch.zeros(2, dtype=torch.int32, device=DEV), torch.zeros(2, 8, device=DEV))
     with pytest.raises(o.KernelError):
         o.swiglu(torch.zeros(2, 7, device=DEV), torch.zeros(2, 3, device=DEV))
-    with pytest.raises(o.KernelError):       # head size above 256
+    with pytest.raises(o.KernelError):       # head size above 640
         z = torch.zeros(1, dtype=torch.int32, device=DEV)
-        o.paged_attention(torch.zeros(1, 272, device=DEV), torch.zeros(1, 1, 4, 272, device=DEV), torch.zeros(1, 1, 4, 272, device=DEV),
-                          torch.zeros(1, 1, dtype=torch.int32, device=DEV), z, z, torch.zeros(1, 272, device=DEV), 1, 1, 272, 4, 0, 1.0)
+        o.paged_attention(torch.zeros(1, 656, device=DEV), torch.zeros(1, 1, 4, 656, device=DEV), torch.zeros(1, 1, 4, 656, device=DEV),
+                          torch.zeros(1, 1, dtype=torch.int32, device=DEV), z, z, torch.zeros(1, 656, device=DEV), 1, 1, 656, 4, 0, 1.0)
 
 
 # ---- the tensor-core matrix products (bfloat16) ---------------------------------------------------
