@@ -168,6 +168,7 @@ def test_work_items_of_a_block_mask_begin_at_the_block_of_their_first_token():
     recs = {(int(r[0]), int(r[1])): (int(r[4]), int(r[5])) for r in items}
     assert recs[(0, 32)] == (0, 37) and recs[(32, 8)] == (30, 45) and recs[(40, 1)] == (30, 38)
     items, merge, info = af.plan_arrays([0, 1, 2], [0, 1, 2], [1, 1, 1], [9, 10, 300], 3, 0, 4, 2, 148, fixed_splits=2, max_context=512, chunk=10)
-    lo = {int(r[3]): min(int(q[4]) for q in items if q[3] == r[3]) for r in items}
-    hi = {int(r[3]): max(int(q[5]) for q in items if q[3] == r[3]) for r in items}
+    full = [q for q in items if q[5] > q[4]]                 # a split past the token's keys is an empty range
+    lo = {int(r[3]): min(int(q[4]) for q in full if q[3] == r[3]) for r in full}
+    hi = {int(r[3]): max(int(q[5]) for q in full if q[3] == r[3]) for r in full}
     assert lo == {9: 0, 10: 10, 300: 300} and hi == {9: 10, 10: 11, 300: 301}
