@@ -1013,8 +1013,10 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
 HK_API int hk_attention_decode_tma(const void* q, const void* k_pages, const void* v_pages, long long num_pages,
                                    const int* block_table, int table_stride, const void* items, int n_items, void* out,
                                    float* part_o, float* part_ml, int H, int G, int hd, int page_tokens, int window,
-                                   float scale_log2, ScoreOpts so, int pages_cap, int* status, void* stream) {
+                                   float scale_log2, int sink, int pages_cap, int* status, const float* sinks, float softcap,
+                                   int chunk, void* stream) {
   if (n_items <= 0) return 0;
+  const ScoreOpts so = make_opts(sink, sinks, softcap, scale_log2, chunk);
   if (G < 1 || H % G != 0 || (H / G) > 16 || G > 65535) return HK_ERR_UNSUPPORTED;
   if ((hd != 64 && hd != 128) || page_tokens < 16 || (page_tokens & (page_tokens - 1))) return HK_ERR_UNSUPPORTED;
   if (((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return HK_ERR_UNSUPPORTED;
