@@ -277,3 +277,39 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
                                         _ptr(out), q.shape[0], H, G, hd, rows, sk, _ptr(sinks), stream)
         ops._check(code, "paged_attention (combine)")
     return True
+
+
+# ---- attention over a compressed cache (csrc/attention_latent.cu) -----------------------------------------------
+
+LATENT_ROWS = 64
+
+
+def latent_supported(H: int, dk: int, dv: int) -> bool:
+    """H query heads over one shared head whose key is a cache row of dk numbers and whose value its first dv."""
+    return 1 <= H <= LATENT_ROWS and dk % 16 == 0 and 16 <= dk <= 576 and dv % 16 == 0 and 16 <= dv <= min(dk, 512)
+
+
+def run_latent(q, pages, block_table, out, H: int, dk: int, dv: int, page_tokens: int, window: int, scale: float,
+               plan: FlashPlan) -> bool:
+    """out bf16 [n, H * dv] from q bf16 [n, H * dk] over the cache rows `pages` [pages, 1, page_tokens, dk]; the plan's
+    items hold at most 64 / H tokens each (a plan made with `plan_arrays(..., H, 1, ...)`)."""
+    from . import ops
+    if not latent_supported(H, dk, dv) or plan is None:
+        return False
+    lib = build.load("attention_latent")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    part_o = part_ml = None
+    if plan.n_parts:
+        part_o = torch.empty((plan.n_parts, LATENT_ROWS, dv), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((plan.n_parts, LATENT_ROWS, 2), dtype=torch.float32, device=q.device)
+    code = lib.hk_attention_latent(_ptr(q), _ptr(pages), _ptr(block_table), int(block_table.shape[1]), _ptr(plan.items),
+                                   plan.n_items, _ptr(out), _ptr(part_o), _ptr(part_ml), H, dk, dv, int(page_tokens), int(window),
+                                   ctypes.c_float(scale * math.log2(math.e)), stream)
+    if code == _UNSUPPORTED:
+        return False
+    ops._check(code, "latent attention")
+    if plan.n_parts:
+        code = lib.hk_attention_latent_combine(_ptr(part_o), _ptr(part_ml), _ptr(plan.first), _ptr(plan.count), _ptr(plan.row0),
+                                               _ptr(out), q.shape[0], H, dv, stream)
+        ops._check(code, "latent attention (combine)")
+    return True

@@ -45,6 +45,7 @@ class LatentAttention(Part):
         self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.c_norm = None
         self._tables_key = None        # set at bind: the flash kernels' work items, when they take a row of this size
         self._sm_count = 0
+        self._wide = False             # set at bind: the row is too wide for the flash kernels, the latent kernel takes it
 
     def _flash_takes(self) -> bool:
         """The flash kernels run H query heads over ONE key/value head whose keys and values are both the cache row
@@ -52,8 +53,15 @@ class LatentAttention(Part):
         from ..csrc import attention_fast
         return attention_fast.supported(self.r + self.dr, self.H)
 
+    def _latent_kernel_takes(self) -> bool:
+        """Wider rows: the kernel that keeps the query tile in shared memory and splits the value columns among warps."""
+        from ..csrc import attention_fast
+        return attention_fast.latent_supported(self.H, self.r + self.dr, self.r)
+
     def kernel_libraries(self, bfloat16: bool):
         from ..csrc import attention_fast
+        if bfloat16 and not self._flash_takes() and self._latent_kernel_takes():
+            return ("attention_latent",)
         if not bfloat16 or not self._flash_takes():
             return ()
         return ("attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.r + self.dr, self.H) \
@@ -64,6 +72,9 @@ class LatentAttention(Part):
 
     def step_tables(self, ctx):
         from .attention import flash_step_tables
+        if self._wide:
+            # items of at most 64 / H tokens, all heads of a token in one item; never the tcgen05 prompt kernels' tiles
+            return flash_step_tables(ctx, self.H, 1, self.r + self.dr, self.window or 0, 0, self._sm_count, plain=False)
         return flash_step_tables(ctx, self.H, 1, self.r + self.dr, self.window or 0, 0, self._sm_count)
 
     def children(self):
@@ -101,6 +112,10 @@ class LatentAttention(Part):
         if precision.compute == torch.bfloat16 and self._flash_takes():
             self._tables_key = ("paged_attention_items", self.window or 0, self.H, 1, self.r + self.dr, False, 0, False)
             self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
+        elif precision.compute == torch.bfloat16 and self._latent_kernel_takes():
+            self._wide = True
+            self._tables_key = ("latent_attention_items", self.window or 0, self.H, self.r + self.dr)
+            self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
 
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
                 accumulate: bool = True) -> None:
@@ -121,7 +136,18 @@ class LatentAttention(Part):
         ops.gemm_heads(q_plain.view(n, H, dn), self.w_uk_t, q_full.view(n, H, r + dr)[:, :, :r], H)
         from .attention import flash_plan
         plan = flash_plan(ctx, self._tables_key) if dt == torch.bfloat16 and ops.forced("attention") != "generic" else None
-        if plan is not None:
+        lat = None
+        if plan is not None and self._wide:
+            from ..csrc import attention_fast
+            lat = torch.empty((n, H * r), dtype=dt, device=dev)
+            if attention_fast.run_latent(q_full, cache.k_pages, cache.block_table, lat, H, r + dr, r, cache.page_tokens,
+                                         self.window or 0, self.scale, plan):
+                lat = lat.view(n, H, r)
+            else:
+                lat = None
+        if lat is not None:
+            pass
+        elif plan is not None and not self._wide:
             # the flash kernels, with the cache rows as keys AND values: the result's first r dims per head are the latent sums
             wide = torch.empty((n, H * (r + dr)), dtype=dt, device=dev)
             ops.paged_attention(q_full, cache.k_pages, cache.k_pages, cache.block_table, ctx.positions, ctx.slot_of_token, wide,

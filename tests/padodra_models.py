@@ -76,8 +76,14 @@ CONFIGS = {
         dict(latent(4, 32, 32, 32, 96, 0.11, ramped(100000.0, 32, 6.0, original=96)), mlp=dense(96)),
         dict(attention(6, 2, 64, 64, 0.125, block=70, cap=12.0, rot=banded(20000.0, 64, 4.0, original=128)), mlp=dense(160)),
     ], 0.08),
+    # a latent row of 160 numbers (wider than a flash head), heads of 128 with four query heads per key head
+    "S": config(96, 180, 1e-6, 4.0, 0.5, [
+        dict(latent(5, 24, 16, 16, 144, 0.09, ramped(40000.0, 16, 3.0, original=48)), mlp=dense(112)),
+        dict(attention(4, 1, 128, 128, 0.09, block=48, cap=25.0, rot=banded(30000.0, 128, 6.0, original=96)), mlp=dense(80)),
+        dict(latent(5, 24, 16, 16, 144, 0.09, ramped(40000.0, 16, 3.0, original=48)), mlp=None),
+    ], 0.08),
 }
-SEEDS = {"P": 31, "Q": 32, "R": 33}
+SEEDS = {"P": 31, "Q": 32, "R": 33, "S": 34}
 
 
 def make_model_dir(tmpdir, which: str, dtype=torch.float32) -> str:

@@ -179,11 +179,18 @@ def test_the_sink_takes_its_share_per_head(dtype):
     (48, 5, 6, 6, 14, 22, 0.35, M.ramped(300.0, 6, 5.0, original=32)),                         # nothing a multiple of 4
     (32, 1, 24, 8, 40, 300, 0.1, M.ramped(10000.0, 8, 2.0, original=8)),                       # one head, a cache row above 256
     (32, 2, 10, 16, 10, 12, 0.3, None),                                                        # no rotation at all
+    # cache rows wider than a flash head (multiples of 16): the kernel with the query tile in shared memory
+    (64, 4, 16, 16, 24, 176, 0.1, M.ramped(10000.0, 16, 4.0, original=32)),                   # values over 2 x 128 columns
+    (48, 3, 32, 64, 16, 512, 0.05, M.ramped(10000.0, 64, 8.0, original=64)),                  # the widest row: 576, values 512
+    (32, 20, 8, 16, 8, 144, 0.15, M.ramped(500.0, 16)),                                        # 20 heads: three tokens a tile
+    (32, 64, 8, 16, 8, 128, 0.15, M.ramped(500.0, 16)),                                        # 64 heads: one token a tile
 ])
 def test_latent_attention_under_every_cut(dtype, d, H, dn, dr, dv, r, scale, rot):
     part, entry = latent_part(d, H, dn, dr, dv, r, scale, rot)
     under_every_cut(part, entry, K.latent_attention, dtype, d)
     assert part.cache_spec().v_dim == 0 and part.cache_spec().k_dim == r + dr and part.cache_spec().n_kv_heads == 1
+    if dtype == torch.bfloat16 and (r + dr) % 16 == 0 and r % 16 == 0:       # a tensor-core kernel took it, not the generic one
+        assert part.step_tables_key() is not None and part._wide == (r + dr > 128)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)

@@ -23,6 +23,7 @@ CASES = {
     "P": dict(lengths=[7, 30, 61, 1, 45], page_tokens=4),
     "Q": dict(lengths=[90, 5, 33, 140], page_tokens=16),
     "R": dict(lengths=[150, 20, 75, 210], page_tokens=16),
+    "S": dict(lengths=[130, 9, 201, 64], page_tokens=16),
 }
 _cache = {}
 
@@ -73,7 +74,7 @@ def compare(got, ref, seqs, dtype, slack=None):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("which", ["P", "Q", "R"])
+@pytest.mark.parametrize("which", ["P", "Q", "R", "S"])
 @pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed", "mixed_tight"])
 def test_replay_matches_plain(tmp_path_factory, which, dtype, family):
     from hk_b200.engine import Engine
@@ -90,7 +91,7 @@ def test_replay_matches_plain(tmp_path_factory, which, dtype, family):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("which", ["P", "R"])
+@pytest.mark.parametrize("which", ["P", "R", "S"])
 def test_captured_decode_steps_equal_eager_ones(tmp_path_factory, which, dtype):
     from hk_b200.engine import Engine
     d, _, _, seqs, _, _ = setup_case(tmp_path_factory, which, dtype)
