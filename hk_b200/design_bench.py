@@ -263,24 +263,170 @@ def kernel_points(width: int, n: int, peaks: dict) -> dict:
     return out
 
 
+def padodra_shape(width: int, groups: int = 2, vocab: int = 32000, block: int = 1024) -> dict:
+    """Layer sizes that resemble a real model's: attention with heads of 128 and four query heads per key head, a soft cap,
+    a mask of blocks of 1,024 positions and a sink; latent attention with per head 128 plain and 64 rotated query dims,
+    values of 128 and a cached latent of 512 (a cache row of 576 numbers); GeGLU feed-forwards of three times the width."""
+    heads = width // 128
+    att = {"type": "attention", "mixer": {"dim": 128, "heads": heads, "kv_heads": max(1, heads // 4), "vdim": 128,
+                                          "mask": {"size": block}, "softcap": 30.0, "scale": 1.0 / math.sqrt(128.0),
+                                          "rot": {"base": 500000.0, "dims": 128,
+                                                  "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    lat = {"type": "latent_attention", "mixer": {"dim": 128, "heads": heads, "kv_rank": 512, "rot_dim": 64, "vdim": 128,
+                                                 "scale": 1.0 / math.sqrt(192.0),
+                                                 "rot": {"base": 10000.0, "dims": 64,
+                                                         "scaling": {"factor": 40.0, "fast": 32.0, "slow": 1.0, "original": 4096}}}}
+    dense = {"kind": "dense", "ff": 3 * width}
+    layers = []
+    for g in range(groups):
+        layers += [dict(att, mlp=dense), dict(lat, mlp=dense), dict(lat, mlp=dense), dict(att, mlp=dense)]
+    return {"architecture": "Padodra", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "embedding": {"scale": math.sqrt(width)},
+            "logit_scale": 0.5, "layers": layers, "initializer_range": 0.02}
+
+
+def padodra_kernel_points(width: int, n: int, context: int, peaks: dict) -> dict:
+    """The design's kernels alone at a layer of this width, each beside the like kernel of the Qwen3 decoder: with
+    context = 0 one request of n prompt tokens, else n requests that each bring one token over `context` cached ones."""
+    import numpy as np
+    import torch
+
+    from .csrc import attention_fast, ops
+    dev = "cuda"
+    bw, tc = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    out = {}
+
+    def note(name, us, nbytes, flops, peak_flops, like=None):
+        floor = max(nbytes / bw, flops / peak_flops if peak_flops else 0.0) * 1e6
+        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "flops": int(flops), "roofline_us": round(floor, 2),
+                     "of_roofline": round(floor / us, 3), **({"like": like} if like else {})}
+
+    H, G, hd, pt, block = width // 128, max(1, width // 512), 128, 64, 1024
+    sm = torch.cuda.get_device_properties(0).multi_processor_count
+    decode = context > 0
+    reqs = n if decode else 1
+    per = (context + 1) if decode else n
+    ppr = -(-per // pt)                                   # pages per request
+    table = torch.arange(reqs * ppr, dtype=torch.int32, device=dev).view(reqs, ppr).contiguous()
+    slots = list(range(reqs))
+    q_starts = list(range(n)) if decode else [0]
+    q_lens = [1] * n if decode else [n]
+    starts = [context] * n if decode else [0]
+    positions = torch.tensor([context] * n if decode else list(range(n)), dtype=torch.int32, device=dev)
+    slot_of = torch.tensor(list(range(n)) if decode else [0] * n, dtype=torch.int32, device=dev)
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    pairs_plain = n * (context + 1) if decode else n * (n + 1) // 2
+    pairs_block = sum(min(p % block, p) + 1 for p in ([context] * n if decode else range(n)))
+
+    # ---- grouped-query attention: with the soft cap, the mask of blocks and the sink; and plain (Qwen3's)
+    kp = (torch.randn(reqs * ppr, G, pt, hd, device=dev) * 0.5).bfloat16()
+    vp = (torch.randn(reqs * ppr, G, pt, hd, device=dev) * 0.5).bfloat16()
+    q = (torch.randn(n, H * hd, device=dev) * 0.5).bfloat16()
+    att = torch.empty(n, H * hd, dtype=torch.bfloat16, device=dev)
+    sinks = torch.zeros(H, device=dev)
+    fixed = attention_fast.decode_splits(n, G, sm) if decode else 0
+    plan = attention_fast.build_plan(slots, q_starts, q_lens, starts, n, 0, H, G, sm, up, fixed_splits=fixed,
+                                     max_context=context + 64 if decode else 0, prefill_rows=64, chunk=block)
+    us = _time_kernel(lambda: ops.paged_attention(q, kp, vp, table, positions, slot_of, att, H, G, hd, pt, 0, hd ** -0.5, plan=plan,
+                                                  sink=True, sinks=sinks, softcap=30.0, chunk=block))
+    keys_read = (min(context % block, context) + 1) * n if decode else n
+    note("attention with cap, blocks and sink", us, keys_read * G * hd * 4 + n * H * hd * 4, 4.0 * pairs_block * H * hd, tc,
+         like="attention (Qwen3)")
+    rows = 256 if (not decode and attention_fast.tc2_prefill_supported(hd, H // G, pt)) else (128 if not decode else 64)
+    plan0 = attention_fast.build_plan(slots, q_starts, q_lens, starts, n, 0, H, G, sm, up, fixed_splits=fixed,
+                                      max_context=context + 64 if decode else 0, prefill_rows=rows)
+    us = _time_kernel(lambda: ops.paged_attention(q, kp, vp, table, positions, slot_of, att, H, G, hd, pt, 0, hd ** -0.5, plan=plan0))
+    note("attention (Qwen3)", us, (n * (context + 1) if decode else n) * G * hd * 4 + n * H * hd * 4, 4.0 * pairs_plain * H * hd, tc)
+    gate = torch.randn(n, H * hd, device=dev)
+    us = _time_kernel(lambda: ops.sigmoid_gate(att, gate, att))
+    note("sigmoid_gate", us, n * H * hd * 8, 0, 0, like="swiglu (Qwen3, unfused form)")
+
+    # ---- latent attention: H heads over one cache row of 576 numbers whose first 512 are the value
+    r, dr, dn, dv = 512, 64, 128, 128
+    dk = r + dr
+    rows_l = (torch.randn(reqs * ppr, 1, pt, dk, device=dev) * 0.3).bfloat16()
+    ql = (torch.randn(n, H * dk, device=dev) * 0.3).bfloat16()
+    lat = torch.empty(n, H * r, dtype=torch.bfloat16, device=dev)
+    fixed_l = attention_fast.decode_splits(n, 1, sm) if decode else 0
+    plan_l = attention_fast.build_plan(slots, q_starts, q_lens, starts, n, 0, H, 1, sm, up, fixed_splits=fixed_l,
+                                       max_context=context + 64 if decode else 0, prefill_rows=64)
+    us = _time_kernel(lambda: attention_fast.run_latent(ql, rows_l, table, lat, H, dk, r, pt, 0, 192 ** -0.5, plan_l))
+    note("latent attention (rows of 576, values of 512)", us, (n * (context + 1) if decode else n) * dk * 2 + n * H * (dk + r) * 2,
+         2.0 * pairs_plain * H * (dk + r), tc, like="attention (Qwen3)")
+    proj = torch.randn(n, H * (dn + dr) + dk + H * dv, device=dev)
+    q_plain = torch.empty(n, H * dn, dtype=torch.bfloat16, device=dev)
+    cn = torch.ones(r, device=dev)
+    cos = torch.ones(per + 1, dr // 2, device=dev)
+    sin = torch.zeros(per + 1, dr // 2, device=dev)
+    us = _time_kernel(lambda: ops.latent_prep(proj, q_plain, ql, cn, 1e-6, cos, sin, dr, "half", positions, slot_of, table, rows_l,
+                                              H, dn, dr, r, pt))
+    note("latent_prep", us, n * (H * (dn + dr) + dk) * 6, 0, 0, like="qk_norm_rope_kv_write (Qwen3)")
+    qkv = torch.randn(n, (H + 2 * G) * hd, device=dev)
+    qn = torch.ones(hd, device=dev)
+    cos2 = torch.ones(per + 1, hd // 2, device=dev)
+    sin2 = torch.zeros(per + 1, hd // 2, device=dev)
+    us = _time_kernel(lambda: ops.qk_norm_rope_kv_write(qkv, q, qn, qn, 1e-6, cos2, sin2, hd, positions, slot_of, table, kp, vp, H, G, hd, pt))
+    note("qk_norm_rope_kv_write (Qwen3)", us, n * (H + 2 * G) * hd * 6, 0, 0)
+    w_uk = (torch.randn(H, r, dn, device=dev) * 0.05).bfloat16()
+    w_uv = (torch.randn(H, dv, r, device=dev) * 0.05).bfloat16()
+    o = torch.empty(n, H * dv, device=dev)
+    us = _time_kernel(lambda: ops.gemm_heads(q_plain.view(n, H, dn), w_uk, ql.view(n, H, dk)[:, :, :r], H))
+    note("query into the latent space (a product per head)", us, H * r * dn * 2 + n * H * (dn + r) * 2, 2.0 * n * H * r * dn, tc,
+         like="dense product of equal FLOPs (Qwen3)")
+    us = _time_kernel(lambda: ops.gemm_heads(lat.view(n, H, r), w_uv, o.view(n, H, dv), H))
+    note("values out of the latent space (a product per head)", us, H * r * dv * 2 + n * H * (r * 2 + dv * 4), 2.0 * n * H * r * dv, tc,
+         like="dense product of equal FLOPs (Qwen3)")
+    wd = (torch.randn(H * dn, r, device=dev) * 0.05).bfloat16()       # [N = H * 128, K = 512]: the same FLOPs as one of the two
+    a2 = (torch.randn(n, r, device=dev) * 0.3).bfloat16()
+    od = torch.empty(n, H * dn, device=dev)
+    us = _time_kernel(lambda: ops.gemm(a2, wd, od))
+    note("dense product of equal FLOPs (Qwen3)", us, H * dn * r * 2 + n * (r * 2 + H * dn * 4), 2.0 * n * H * dn * r, tc)
+
+    # ---- the layer's row-wise kernels and the feed-forward's first product
+    x = torch.randn(n, width, device=dev)
+    res = torch.randn(n, width, device=dev)
+    wn = torch.ones(width, device=dev)
+    xb = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
+    us = _time_kernel(lambda: ops.rms_norm_add(x, wn, 1e-6, res, xb))
+    note("rms_norm_add with the narrowed copy", us, n * width * 14, 0, 0, like="rms_norm (Qwen3)")
+    us = _time_kernel(lambda: ops.rms_norm(x, wn, 1e-6, xb))
+    note("rms_norm (Qwen3)", us, n * width * 6, 0, 0)
+    F = 3 * width
+    wgu = (torch.randn(2 * F, width, device=dev) * 0.02).bfloat16()
+    xb.copy_(torch.randn(n, width, device=dev))
+    hb = torch.empty(n, F, dtype=torch.bfloat16, device=dev)
+    for act, name in (("gelu_tanh", "gate/up product with the gelu gate in its epilogue"), ("silu", "gate/up product with SwiGLU epilogue (Qwen3)")):
+        us = _time_kernel(lambda: ops.gemm_swiglu(xb, wgu, hb, act))
+        note(name, us, 2 * F * width * 2 + n * (width + F) * 2, 4.0 * n * F * width, tc,
+             like=None if act == "silu" else "gate/up product with SwiGLU epilogue (Qwen3)")
+    gu = torch.randn(n, 2 * F, device=dev)
+    us = _time_kernel(lambda: ops.swiglu(gu, hb))
+    note("swiglu (Qwen3, unfused form)", us, n * F * 10, 0, 0)
+    return out
+
+
 def run(design: str, args, peaks: dict) -> dict:
-    if design != "kedanex":
-        raise SystemExit(f"bench.py --design: unknown design '{design}' (known: kedanex)")
+    if design not in ("kedanex", "padodra"):
+        raise SystemExit(f"bench.py --design: unknown design '{design}' (known: kedanex, padodra)")
     widths = [int(w) for w in str(args.design_widths).split(",")]
     sizes = {}
     for width in widths:
         t0 = time.time()
-        ours = kedanex_shape(width)
+        ours = kedanex_shape(width) if design == "kedanex" else padodra_shape(width)
         theirs = qwen3_shape(width, len(ours["layers"]))
-        entry = {"kedanex": model_points(ours, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
+        entry = {design: model_points(ours, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
                  "qwen3": model_points(theirs, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
                  "layer_runs": len(ours["layers"])}
-        entry["kernels_prefill_2048_rows"] = kernel_points(width, 2048, peaks)
-        entry["kernels_decode_64_rows"] = {k: v for k, v in kernel_points(width, 64, peaks).items() if "request" not in k or "decode" in k}
+        if design == "kedanex":
+            entry["kernels_prefill_2048_rows"] = kernel_points(width, 2048, peaks)
+            entry["kernels_decode_64_rows"] = {k: v for k, v in kernel_points(width, 64, peaks).items() if "request" not in k or "decode" in k}
+        else:
+            entry["kernels_prefill_2048_rows"] = padodra_kernel_points(width, 2048, 0, peaks)
+            entry["kernels_decode_64_rows"] = padodra_kernel_points(width, 64, 2047, peaks)
+            entry["kernels_decode_8_rows"] = padodra_kernel_points(width, 8, 2047, peaks)
         sizes[f"width{width}"] = entry
         print(f"[bench] design {design}, width {width}: {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
     k = sizes[f"width{widths[-1]}"]
-    return {"metric": f"{design} prefill and decode tok/s beside Qwen3 at equal width and depth", "value": k["kedanex"]["decode_b8"]["tok_s"],
+    return {"metric": f"{design} prefill and decode tok/s beside Qwen3 at equal width and depth", "value": k[design]["decode_b8"]["tok_s"],
             "unit": "tokens/s (decode, batch 8, largest width)", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
             "higher_is_better": True, "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random-init weights",
             "impl": "ours", "design": design, "sizes": sizes, "peaks": peaks}
