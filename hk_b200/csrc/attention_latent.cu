@@ -124,6 +124,7 @@ latent_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, 
 
   const int t_begin = it.kv_lo / TK;
   const int t_end = (it.kv_hi + TK - 1) / TK;
+  const bool active = rg * 16 < it.n_tokens * H;      // whether any of this warp's 16 rows is a (token, head) of the item
 
   auto load_tile = [&](int t, int stage) {
     bf16* kd = ks + stage * TK * LD;
@@ -156,6 +157,10 @@ latent_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, 
     cp_async_wait<1>();
     __syncthreads();
     const bf16* kt = ks + stage * TK * LD;
+    if (!active) {             // a decode step fills few of the 64 rows: the other row groups only help with the loads
+      __syncthreads();
+      continue;
+    }
 
     // ---- scores: this warp's 16 rows against its 16 keys of the tile, over all DK columns
     float s[2][4];

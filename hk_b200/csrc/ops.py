@@ -449,6 +449,14 @@ def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_heads: int
     N = out.shape[2]
     if tuple(w.shape) != (H, N, K) or out.shape[0] != n:
         raise KernelError("gemm_heads: shapes do not fit")
+    if a.dtype == torch.bfloat16 and _forced["gemm"] != "generic":
+        lib = build.load("gemm_heads")
+        code = lib.hk_gemm_heads_mma(_ptr(a), _ptr(w), _ptr(out), _dt(out), n, N, K, H, ctypes.c_longlong(a.stride(0)),
+                                     ctypes.c_longlong(a.stride(1)), ctypes.c_longlong(out.stride(0)),
+                                     ctypes.c_longlong(out.stride(1)), _stream())
+        if code != _ERR_UNSUPPORTED:
+            _check(code, "gemm_heads (mma)")
+            return
     lib = build.load("gemm_generic")
     _check(lib.hk_gemm_heads(_ptr(a), _ptr(w), _dt(a), _ptr(out), _dt(out), n, N, K, H, ctypes.c_longlong(a.stride(0)),
                              ctypes.c_longlong(a.stride(1)), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)),

@@ -60,12 +60,12 @@ class LatentAttention(Part):
 
     def kernel_libraries(self, bfloat16: bool):
         from ..csrc import attention_fast
-        if bfloat16 and not self._flash_takes() and self._latent_kernel_takes():
-            return ("attention_latent",)
-        if not bfloat16 or not self._flash_takes():
+        if not bfloat16:
             return ()
-        return ("attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.r + self.dr, self.H) \
-            else ("attention_flash",)
+        if not self._flash_takes():
+            return ("gemm_heads", "attention_latent") if self._latent_kernel_takes() else ("gemm_heads",)
+        return ("gemm_heads", "attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.r + self.dr, self.H) \
+            else ("gemm_heads", "attention_flash")
 
     def step_tables_key(self):
         return self._tables_key

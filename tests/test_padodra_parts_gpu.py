@@ -276,3 +276,45 @@ def test_post_norm_block_embedding_scale_and_logit_scale(dtype, d):
     close(np.concatenate(got), want, dtype)
     plain = dict(raw, embedding={"scale": 1.0})
     assert np.abs(K.forward(plain, w, ids) - want).max() > 0.05 * np.abs(want).max()
+
+
+# ------------------------------------------------------------------------------------ the kernels underneath
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("n,H,K,N", [(1, 3, 16, 24), (70, 2, 128, 512), (9, 5, 40, 12), (130, 4, 512, 128), (64, 1, 8, 8), (33, 6, 6, 10)])
+def test_a_product_per_head_over_slices_of_wider_rows(dtype, n, H, K, N):
+    """out[t, h] = a[t, h] W_h^T where a and out are the first columns of wider heads, in the type's tensor-core kernel
+    (bfloat16, sizes it takes) and in the plain one."""
+    from hk_b200.csrc import ops
+    g = torch.Generator().manual_seed(n * 7 + K)
+    a_wide = torch.randn(n, H, K + 8, generator=g).to(dtype).cuda()
+    w = (torch.randn(H, N, K, generator=g) * 0.2).to(dtype).cuda()
+    want = np.einsum("thk,hnk->thn", a_wide[:, :, :K].double().cpu().numpy(), w.double().cpu().numpy())
+    for out_dtype in ({dtype, torch.float32}):
+        out_wide = torch.full((n, H, N + 6), 7.0, dtype=out_dtype, device="cuda")
+        ops.gemm_heads(a_wide[:, :, :K], w, out_wide[:, :, :N], H)
+        close(out_wide[:, :, :N].double().cpu().numpy(), want, dtype)
+        assert (out_wide[:, :, N:] == 7.0).all()                   # nothing beside the slice was touched
+        with ops.force(gemm="generic"):
+            again = torch.zeros((n, H, N), dtype=out_dtype, device="cuda")
+            ops.gemm_heads(a_wide[:, :, :K], w, again, H)
+        close(again.double().cpu().numpy(), want, dtype)
+
+
+@pytest.mark.parametrize("d", [48, 512, 1000, 4096])
+def test_rows_written_with_their_narrowed_copy(d):
+    """The embedding (with its factor) and the norm + residual sum also leave the new rows rounded to bfloat16."""
+    from hk_b200.csrc import ops
+    table = torch.randn(50, d, device="cuda").to(torch.bfloat16)
+    ids = torch.tensor([3, 49, 0, 3, 17], dtype=torch.int32, device="cuda")
+    x = torch.empty(5, d, device="cuda")
+    xb = torch.empty(5, d, dtype=torch.bfloat16, device="cuda")
+    ops.embedding(table, ids, x, 2.7, xb)
+    want = table[ids.long()].float() * 2.7
+    assert torch.equal(x, want) and torch.equal(xb, want.to(torch.bfloat16))
+    y, w = torch.randn(5, d, device="cuda"), torch.rand(d, device="cuda") + 0.5
+    res = x.clone()
+    ops.rms_norm_add(y, w, 1e-5, res, xb)
+    want = x.double() + y.double() / torch.sqrt((y.double() ** 2).mean(-1, keepdim=True) + 1e-5) * w.double()
+    assert torch.allclose(res.double(), want, rtol=1e-5, atol=1e-5) and torch.equal(xb, res.to(torch.bfloat16))
