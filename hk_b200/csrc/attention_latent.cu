@@ -90,7 +90,9 @@ latent_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, 
 
   const Item it = items[blockIdx.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rg = warp & 3, half = warp >> 2;
+  // the two warps of a row group are neighbours, so they sit on different tensor units of the SM: a decode step, which
+  // fills one or two row groups, still keeps two or four of the four units busy
+  const int rg = warp >> 1, half = warp & 1;
   const int qr = lane >> 2, qt = lane & 3;
   const int mi = lane >> 3, r8 = lane & 7;
   const int* bt = block_table + (size_t)it.slot * table_stride;
@@ -162,22 +164,39 @@ latent_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, 
       continue;
     }
 
-    // ---- scores: this warp's 16 rows against its 16 keys of the tile, over all DK columns
+    // ---- scores: this warp's 16 rows against its 16 keys of the tile, over all DK columns.  Four K slices at a time:
+    // their eight fragment loads go out before the eight products that use them, and every fourth slice adds onto the
+    // same partial sums, so a product never waits for the one before it.
+    float sp[4][2][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sp[u][n][e] = 0.f;
+    const bf16* qa = qs + (rg * 16 + r8 + (mi & 1) * 8) * LD + (mi >> 1) * 8;
+    const bf16* kb = kt + (half * 16 + (mi >> 1) * 8 + r8) * LD + (mi & 1) * 8;
+    const int ksteps = DK / 16;
+    for (int kk0 = 0; kk0 < ksteps; kk0 += 4) {
+      uint32_t a[4][4], b[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (kk0 + u < ksteps) {
+          ldmatrix_x4(a[u], qa + (kk0 + u) * 16);
+          ldmatrix_x4(b[u], kb + (kk0 + u) * 16);
+        }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (kk0 + u < ksteps) {
+          mma_bf16(sp[u][0], a[u], b[u][0], b[u][1]);
+          mma_bf16(sp[u][1], a[u], b[u][2], b[u][3]);
+        }
+    }
     float s[2][4];
 #pragma unroll
     for (int n = 0; n < 2; ++n)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
-    const bf16* qa = qs + (rg * 16 + r8 + (mi & 1) * 8) * LD + (mi >> 1) * 8;
-    const bf16* kb = kt + (half * 16 + (mi >> 1) * 8 + r8) * LD + (mi & 1) * 8;
-#pragma unroll 4
-    for (int kk = 0; kk < DK / 16; ++kk) {
-      uint32_t a[4], b[4];
-      ldmatrix_x4(a, qa + kk * 16);
-      ldmatrix_x4(b, kb + kk * 16);
-      mma_bf16(s[0], a, b[0], b[1]);
-      mma_bf16(s[1], a, b[2], b[3]);
-    }
+      for (int e = 0; e < 4; ++e) s[n][e] = (sp[0][n][e] + sp[1][n][e]) + (sp[2][n][e] + sp[3][n][e]);
     float mt[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
     for (int n = 0; n < 2; ++n)
@@ -232,13 +251,17 @@ latent_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, 
       ldmatrix_x4(pf, pa + kk * 16);
       const bf16* vb = kt + (kk * 16 + (mi & 1) * 8 + r8) * LD + half * DVW + (mi >> 1) * 8;
 #pragma unroll
-      for (int dp = 0; dp < DVW / 16; ++dp) {
-        if (half * DVW + dp * 16 < DV) {
-          uint32_t b[4];
-          ldmatrix_x4_trans(b, vb + dp * 16);
-          mma_bf16(o[2 * dp], pf, b[0], b[1]);
-          mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
-        }
+      for (int dp0 = 0; dp0 < DVW / 16; dp0 += 4) {       // four column pairs at a time: loads first, then the products
+        uint32_t b[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (half * DVW + (dp0 + u) * 16 < DV) ldmatrix_x4_trans(b[u], vb + (dp0 + u) * 16);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (half * DVW + (dp0 + u) * 16 < DV) {
+            mma_bf16(o[2 * (dp0 + u)], pf, b[u][0], b[u][1]);
+            mma_bf16(o[2 * (dp0 + u) + 1], pf, b[u][2], b[u][3]);
+          }
       }
     }
     __syncthreads();   // the stage, the maxima and the probability tile are free again
