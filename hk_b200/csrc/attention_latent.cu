@@ -109,12 +109,12 @@ latent_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, 
   }
 
   // the query tile: rows past the item's tokens are zero
-  for (int idx = threadIdx.x; idx < ROWS * CPR; idx += 256) {
-    const int r = idx / CPR, c = idx % CPR;
+  // (a warp copies whole rows, a lane every 32nd chunk of a row: no division in the copy loops)
+  for (int r = warp; r < ROWS; r += 8) {
     const int tq = r / H;
     const bool ok = tq < it.n_tokens;
-    const bf16* src = q + ((size_t)(it.q_row0 + (ok ? tq : 0)) * H + r % H) * DK + c * 8;
-    cp_async16(qs + r * LD + c * 8, src, ok);
+    const bf16* src = q + ((size_t)(it.q_row0 + (ok ? tq : 0)) * H + (r - tq * H)) * DK;
+    for (int c = lane; c < CPR; c += 32) cp_async16(qs + r * LD + c * 8, src + c * 8, ok);
   }
 
   float o[DVW / 8][4];
@@ -142,11 +142,12 @@ latent_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, 
       pg[threadIdx.x] = row_of_key;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < TK * CPR; idx += 256) {
-      const int r = idx / CPR, c = idx % CPR;
+#pragma unroll
+    for (int r = warp; r < TK; r += 8) {
       const int row_of_key = pg[r];
       const bool ok = row_of_key >= 0;
-      cp_async16(kd + r * LD + c * 8, pages + (ok ? (size_t)row_of_key * DK + c * 8 : 0), ok);
+      const bf16* src = pages + (ok ? (size_t)row_of_key * DK : 0);
+      for (int c = lane; c < CPR; c += 32) cp_async16(kd + r * LD + c * 8, src + c * 8, ok);
     }
   };
 
