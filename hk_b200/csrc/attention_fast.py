@@ -43,14 +43,8 @@ def supported(hd: int, group: int) -> bool:
 
 def options_supported(softcap: float, chunk: int, sink_weights: bool) -> bool:
     """Whether the flash kernels know these options of the scores (a bound on the scores, a block-wise mask, a learned
-    score for the sink): the mma.sync prompt kernel and both decode kernels do; the tcgen05 prompt kernels do not, and
-    a mixer that uses any of them (or a sink) is not given those (`plain_scores`)."""
+    score for the sink): all of them do (the mma.sync and the tcgen05 prompt kernels, both decode kernels)."""
     return True
-
-
-def plain_scores(sink: bool, softcap: float, chunk: int) -> bool:
-    """Scores that the tcgen05 prompt kernels compute: scale, causality and a window, nothing else."""
-    return not (sink or softcap or chunk)
 
 
 def tc_prefill_supported(hd: int, group: int) -> bool:
@@ -223,7 +217,6 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
     if not supported(hd, H // G) or plan is None:
         return False
     sk = 1 if sink else 0
-    plain = plain_scores(sink, softcap, chunk)
     extra = (_ptr(sinks), ctypes.c_float(softcap), int(chunk))
     lib = build.load("attention_flash")
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -233,26 +226,26 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
         part_o = torch.empty((plan.n_parts, G, rows, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((plan.n_parts, G, rows, 2), dtype=torch.float32, device=q.device)
     if plan.nw == 16:
-        if not plain or plan.n_parts or not tc2_prefill_supported(hd, H // G, int(page_tokens)):
+        if plan.n_parts or not tc2_prefill_supported(hd, H // G, int(page_tokens)):
             return False
         lib_tc = build.load("attention_prefill_tc")
         code = lib_tc.hk_attention_prefill_tc2(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), ctypes.c_longlong(k_pages.shape[0]), _ptr(block_table),
             int(block_table.shape[1]), _ptr(plan.items), plan.n_items, _ptr(out), H, G, hd, int(page_tokens), int(window),
             ctypes.c_float(scale * math.log2(math.e)), plan.max_keys // int(page_tokens) + 2,
-            _ptr(gemm_fast.status_flag(q.device)), stream)
+            _ptr(gemm_fast.status_flag(q.device)), sk, *extra, stream)
         if code == _UNSUPPORTED:
             return False
         ops._check(code, "paged_attention (tcgen05 prefill, two query tiles)")
         return True
     if plan.nw == 8:
-        if not plain or plan.n_parts or not tc_prefill_supported(hd, H // G):
+        if plan.n_parts or not tc_prefill_supported(hd, H // G):
             return False
         lib_tc = build.load("attention_prefill_tc")
         code = lib_tc.hk_attention_prefill_tc(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), int(block_table.shape[1]), _ptr(plan.items),
             plan.n_items, _ptr(out), H, G, hd, int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)),
-            plan.max_keys // int(page_tokens) + 2, _ptr(gemm_fast.status_flag(q.device)), stream)
+            plan.max_keys // int(page_tokens) + 2, _ptr(gemm_fast.status_flag(q.device)), sk, *extra, stream)
         if code == _UNSUPPORTED:
             return False
         ops._check(code, "paged_attention (tcgen05 prefill)")

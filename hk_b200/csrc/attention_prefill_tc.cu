@@ -45,6 +45,25 @@ struct Item {
   int q_row0, n_tokens, slot, pos0, kv_lo, kv_hi, part, pad;
 };
 
+// What a mixer may ask of the scores beyond scale, window and causality; everything off at zero / null (the same
+// options as the flash kernels take).
+struct ScoreOpts {
+  int sink;             // 1: one more term in the softmax's denominator, a key without a value
+  const float* sinks;   // its score per query head (natural units); null: 0
+  float cap_log2;       // soft cap c on the scores, times log2(e): s <- c tanh(s / c); 0: none
+  float cap_in;         // scale / c
+  int chunk;            // a row at position p sees no key before (p / chunk) * chunk; 0: no such mask
+};
+
+// a raw dot product (or -inf for a masked key) into the capped score in the base-2 exponent domain
+__device__ __forceinline__ uint32_t capped_score(uint32_t raw, const ScoreOpts& so) {
+  const float x = __uint_as_float(raw);
+  const float t = exp2f(2.8853900817779268f * x * so.cap_in);        // e^(2 x scale / c)
+  const float y = so.cap_log2 * (1.0f - __fdividef(2.0f, t + 1.0f));  // c log2(e) tanh(x scale / c)
+  return raw == 0xff800000u ? raw : __float_as_uint(y);
+}
+
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -179,7 +198,7 @@ template <int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                             const int* __restrict__ block_table, int table_stride, const Item* __restrict__ items,
-                            bf16* __restrict__ out, int H, int G, int page_tokens, int window, float scale_log2,
+                            bf16* __restrict__ out, int H, int G, int page_tokens, int window, float scale_log2, ScoreOpts so,
                             int pages_cap, int* __restrict__ status) {
   constexpr int CPR = HD / 8;              // 16-byte chunks per row
   constexpr int KSTEPS = HD / 16;          // MMA k-steps over the head dimension
@@ -369,7 +388,9 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int tq = r / group;
     const bool valid = r < n_rows;
     const int pos = it.pos0 + (valid ? tq : 0);
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (so.chunk > 0) lo = max(lo, (pos / so.chunk) * so.chunk);
+    const float sl = so.cap_log2 > 0.f ? 1.0f : scale_log2;      // capped scores are in the exponent's domain already
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     constexpr int HK = TK / 2, HO = HD / 2;          // keys and O columns per thread
     float m = -CUDART_INF_F, l = 0.f;
@@ -396,13 +417,17 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
           if (!see) su[i] = 0xff800000u;             // -inf
         }
       }
+      if (so.cap_log2 > 0.f) {
+#pragma unroll
+        for (int i = 0; i < HK; ++i) su[i] = capped_score(su[i], so);
+      }
       float mraw = -CUDART_INF_F;
 #pragma unroll
       for (int i = 0; i < HK; ++i) mraw = fmaxf(mraw, __uint_as_float(su[i]));
       sm.xmax[n & 1][half][r] = mraw;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");     // the two warps of this quarter
       mraw = fmaxf(mraw, sm.xmax[n & 1][half ^ 1][r]);
-      const float mt = mraw * scale_log2;
+      const float mt = mraw * sl;
       // Lazy rescaling: the exponentials are taken against a reference maximum `m` that only moves when the row's
       // true maximum has run ahead of it by more than 2^8 (P then stays below 256, exact in bf16's range, and
       // sum and O stay consistent with it, so the result is the same).  Moving it costs a pass over the O row
@@ -423,8 +448,8 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
       uint32_t pw[HK / 2];
 #pragma unroll
       for (int e = 0; e < HK / 2; ++e) {
-        const float p0 = ex2(fmaf(__uint_as_float(su[2 * e]), scale_log2, -msafe));
-        const float p1 = ex2(fmaf(__uint_as_float(su[2 * e + 1]), scale_log2, -msafe));
+        const float p0 = ex2(fmaf(__uint_as_float(su[2 * e]), sl, -msafe));
+        const float p1 = ex2(fmaf(__uint_as_float(su[2 * e + 1]), sl, -msafe));
         l += p0 + p1;
         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
         pw[e] = *reinterpret_cast<uint32_t*>(&pk);
@@ -451,6 +476,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     sm.xsum[half][r] = l;
     asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
     l += sm.xsum[half ^ 1][r];
+    if (so.sink && valid) l += exp2f((so.sinks ? so.sinks[g * group + r % group] * 1.4426950408889634f : 0.f) - m);
     const int last = t_end - t_begin - 1;
     if (ok && last >= 0 && __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[last & 1], (uint32_t)((last >> 1) & 1), abort_flag))) {
       tc_fence_after();
@@ -488,7 +514,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 
 template <int HD>
 int launch(const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items, void* out,
-           int H, int G, int pt, int window, float scale_log2, int pages_cap, int* status, cudaStream_t s) {
+           int H, int G, int pt, int window, float scale_log2, ScoreOpts so, int pages_cap, int* status, cudaStream_t s) {
   const size_t smem = sizeof(Smem<HD>) + 1024 + (size_t)pages_cap * sizeof(int);
   if (smem > 225 * 1024) return HK_ERR_UNSUPPORTED;
   static HkSmemCache allowed = {};
@@ -496,7 +522,7 @@ int launch(const void* q, const void* kp, const void* vp, const int* bt, int str
   dim3 grid((unsigned)n_items * (unsigned)G);
   attention_prefill_tc_kernel<HD><<<grid, NUM_THREADS, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                                  (const Item*)items, (bf16*)out, H, G, pt, window, scale_log2,
-                                                                 pages_cap, status);
+                                                                 so, pages_cap, status);
   return hk_launch_status();
 }
 
@@ -549,7 +575,7 @@ __global__ void __launch_bounds__(NT2, 1)
 attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                              const bf16* __restrict__ q, const int* __restrict__ block_table, int table_stride,
                              const Item* __restrict__ items, bf16* __restrict__ out, int H, int G, int page_tokens, int window,
-                             float scale_log2, int pages_cap, int* __restrict__ status) {
+                             float scale_log2, ScoreOpts so, int pages_cap, int* __restrict__ status) {
   constexpr int CPR = HD / 8;
   constexpr int KSTEPS = HD / 16;
   constexpr int HALVES = HD / 64;
@@ -713,7 +739,9 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __
     const int tq = row / group;
     const bool valid = row < n_rows;
     const int pos = it.pos0 + (valid ? tq : 0);
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (so.chunk > 0) lo = max(lo, (pos / so.chunk) * so.chunk);
+    const float sl = so.cap_log2 > 0.f ? 1.0f : scale_log2;      // capped scores are in the exponent's domain already
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     cp_async_wait<0>();
     fence_async_proxy();
@@ -748,13 +776,17 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __
               if (!see) su[i] = 0xff800000u;             // -inf
             }
           }
+          if (so.cap_log2 > 0.f) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) su[i] = capped_score(su[i], so);
+          }
           float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], fmaxf(__uint_as_float(su[i + 2 * e]), __uint_as_float(su[i + 2 * e + 1])));
           }
-          const float cm = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+          const float cm = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sl;
           const bool move = cm > m + 8.0f;
           if (__any_sync(0xffffffffu, move)) {
             const float mn = move ? ceilf(cm) : m;
@@ -793,8 +825,8 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __
           uint32_t pw[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            const float p0 = ex2(fmaf(__uint_as_float(su[2 * e]), scale_log2, -msafe));
-            const float p1 = ex2(fmaf(__uint_as_float(su[2 * e + 1]), scale_log2, -msafe));
+            const float p0 = ex2(fmaf(__uint_as_float(su[2 * e]), sl, -msafe));
+            const float p1 = ex2(fmaf(__uint_as_float(su[2 * e + 1]), sl, -msafe));
             l0 += p0;
             l1 += p1;
             __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
@@ -809,7 +841,8 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __
       }
       if (ok && n_tiles > 0 && __all_sync(0xffffffffu, mbar_wait(&sm.o_done[qt], 0, abort_flag))) {
         tc_fence_after();
-        const float l = l0 + l1;
+        float l = l0 + l1;
+        if (so.sink && valid) l += exp2f((so.sinks ? so.sinks[g * group + row % group] * 1.4426950408889634f : 0.f) - m);
         const float inv = l > 0.f ? 1.0f / l : 0.f;
         bf16* op = out + ((size_t)(it.q_row0 + (valid ? tq : 0)) * H + g * group + (valid ? row % group : 0)) * HD;
         // the whole row of O at once (the registers that held scores are free now): one wait instead of HD / 32
@@ -875,14 +908,23 @@ bool make_page_map(CUtensorMap* map, const void* ptr, unsigned long long rows, i
 
 template <int HD>
 int launch2(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int* bt, int stride, const void* items, int n_items,
-            void* out, int H, int G, int pt, int window, float scale_log2, int pages_cap, int* status, cudaStream_t s) {
+            void* out, int H, int G, int pt, int window, float scale_log2, ScoreOpts so, int pages_cap, int* status, cudaStream_t s) {
   const size_t smem = sizeof(Smem2<HD>) + 1024 + (size_t)pages_cap * sizeof(int);
   if (smem > 225 * 1024) return HK_ERR_UNSUPPORTED;
   static HkSmemCache allowed = {};
   if (int e = hk_allow_smem(attention_prefill_tc2_kernel<HD>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items * (unsigned)G);
   return hk_launch(attention_prefill_tc2_kernel<HD>, grid, dim3(NT2), smem, s, mk, mv, (const bf16*)q, bt, stride, (const Item*)items,
-                   (bf16*)out, H, G, pt, window, scale_log2, pages_cap, status);
+                   (bf16*)out, H, G, pt, window, scale_log2, so, pages_cap, status);
+}
+
+ScoreOpts make_opts(int sink, const float* sinks, float softcap, float scale_log2, int chunk) {
+  ScoreOpts so = {sink, sink ? sinks : nullptr, 0.f, 0.f, chunk > 0 ? chunk : 0};
+  if (softcap > 0.f) {
+    so.cap_log2 = softcap * 1.4426950408889634f;
+    so.cap_in = scale_log2 / so.cap_log2;       // scale / softcap
+  }
+  return so;
 }
 
 }  // namespace
@@ -890,16 +932,19 @@ int launch2(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const i
 // items: n_items records of 8 ints {first query row, query tokens (at most 128 / (H / G)), request slot, position
 // of the first token, first key, one past the last key, -1, 0}.  pages_cap: the most pages an item's key range spans.  Writes out[token, head, :] directly (no key
 // splitting).  `status` is a device int set to 3 if a wait timed out.  Refuses (HK_ERR_UNSUPPORTED) head sizes
-// other than 64 and 128 and groups above 128 heads.
+// other than 64 and 128 and groups above 128 heads.  sink, sinks, softcap, chunk: see `ScoreOpts` (sinks: one score per
+// query head or null; softcap and chunk 0 for none).
 HK_API int hk_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                    int table_stride, const void* items, int n_items, void* out, int H, int G, int hd,
-                                   int page_tokens, int window, float scale_log2, int pages_cap, int* status, void* stream) {
+                                   int page_tokens, int window, float scale_log2, int pages_cap, int* status, int sink,
+                                   const float* sinks, float softcap, int chunk, void* stream) {
   if (n_items <= 0) return 0;
+  const ScoreOpts so = make_opts(sink, sinks, softcap, scale_log2, chunk);
   if (G < 1 || H % G != 0 || (H / G) > ROWS || G > 65535 || page_tokens < 1 || !(scale_log2 > 0.f)) return HK_ERR_UNSUPPORTED;
   if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-  if (hd == 128) return launch<128>(q, k_pages, v_pages, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
-  if (hd == 64) return launch<64>(q, k_pages, v_pages, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
+  if (hd == 128) return launch<128>(q, k_pages, v_pages, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, so, pages_cap, status, s);
+  if (hd == 64) return launch<64>(q, k_pages, v_pages, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, so, pages_cap, status, s);
   return HK_ERR_UNSUPPORTED;
 }
 
@@ -909,8 +954,9 @@ HK_API int hk_attention_prefill_tc(const void* q, const void* k_pages, const voi
 HK_API int hk_attention_prefill_tc2(const void* q, const void* k_pages, const void* v_pages, long long num_pages,
                                     const int* block_table, int table_stride, const void* items, int n_items, void* out, int H,
                                     int G, int hd, int page_tokens, int window, float scale_log2, int pages_cap, int* status,
-                                    void* stream) {
+                                    int sink, const float* sinks, float softcap, int chunk, void* stream) {
   if (n_items <= 0) return 0;
+  const ScoreOpts so = make_opts(sink, sinks, softcap, scale_log2, chunk);
   if (G < 1 || H % G != 0 || (H / G) > ROWS || G > 65535 || page_tokens < 1 || !(scale_log2 > 0.f)) return HK_ERR_UNSUPPORTED;
   if (hd != 64 && hd != 128) return HK_ERR_UNSUPPORTED;
   const bool boxes_ok = (page_tokens % 8 == 0 && TK % page_tokens == 0) || page_tokens % TK == 0;
@@ -921,7 +967,7 @@ HK_API int hk_attention_prefill_tc2(const void* q, const void* k_pages, const vo
   CUtensorMap mk, mv;
   if (!make_page_map(&mk, k_pages, rows, hd, box_rows) || !make_page_map(&mv, v_pages, rows, hd, box_rows)) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-  if (hd == 128) return launch2<128>(mk, mv, q, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
-  return launch2<64>(mk, mv, q, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
+  if (hd == 128) return launch2<128>(mk, mv, q, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, so, pages_cap, status, s);
+  return launch2<64>(mk, mv, q, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, so, pages_cap, status, s);
 }
 

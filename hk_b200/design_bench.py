@@ -324,14 +324,14 @@ def padodra_kernel_points(width: int, n: int, context: int, peaks: dict) -> dict
     att = torch.empty(n, H * hd, dtype=torch.bfloat16, device=dev)
     sinks = torch.zeros(H, device=dev)
     fixed = attention_fast.decode_splits(n, G, sm) if decode else 0
+    rows = 256 if (not decode and attention_fast.tc2_prefill_supported(hd, H // G, pt)) else (128 if not decode else 64)
     plan = attention_fast.build_plan(slots, q_starts, q_lens, starts, n, 0, H, G, sm, up, fixed_splits=fixed,
-                                     max_context=context + 64 if decode else 0, prefill_rows=64, chunk=block)
+                                     max_context=context + 64 if decode else 0, prefill_rows=rows, chunk=block)
     us = _time_kernel(lambda: ops.paged_attention(q, kp, vp, table, positions, slot_of, att, H, G, hd, pt, 0, hd ** -0.5, plan=plan,
                                                   sink=True, sinks=sinks, softcap=30.0, chunk=block))
     keys_read = (min(context % block, context) + 1) * n if decode else n
     note("attention with cap, blocks and sink", us, keys_read * G * hd * 4 + n * H * hd * 4, 4.0 * pairs_block * H * hd, tc,
          like="attention (Qwen3)")
-    rows = 256 if (not decode and attention_fast.tc2_prefill_supported(hd, H // G, pt)) else (128 if not decode else 64)
     plan0 = attention_fast.build_plan(slots, q_starts, q_lens, starts, n, 0, H, G, sm, up, fixed_splits=fixed,
                                       max_context=context + 64 if decode else 0, prefill_rows=rows)
     us = _time_kernel(lambda: ops.paged_attention(q, kp, vp, table, positions, slot_of, att, H, G, hd, pt, 0, hd ** -0.5, plan=plan0))

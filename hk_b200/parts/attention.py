@@ -43,12 +43,11 @@ from .base import KVCacheSpec, MATRIX, VECTOR, ParamSpec, Part, Precision, StepT
 from .position import RotaryEmbedding
 
 
-def flash_step_tables(ctx, H: int, G: int, hd: int, window: int, chunk: int, sm_count: int, plain: bool = True):
-    """The flash kernels' work items for one step, as a part's host-built tables.  `plain`: the scores are scale,
-    causality and a window alone, which is what the tcgen05 prompt kernels compute; a mixer that asks more of its
-    scores (a sink, a cap, a mask of blocks) takes the mma.sync flash kernel for prompts."""
+def flash_step_tables(ctx, H: int, G: int, hd: int, window: int, chunk: int, sm_count: int, tensor_prompt: bool = True):
+    """The flash kernels' work items for one step, as a part's host-built tables.  `tensor_prompt` = False keeps prompt
+    portions off the tcgen05 kernels' tiles of 128 and 256 rows (for a kernel of its own that takes 64-row items)."""
     from ..csrc import attention_fast
-    tc = attention_fast.tc_prefill_supported(hd, H // G) and ops.forced("attention") != "flash_cp" and plain
+    tc = attention_fast.tc_prefill_supported(hd, H // G) and ops.forced("attention") != "flash_cp" and tensor_prompt
     rows = 128 if tc else 64
     # the kernel with two query tiles per CTA is the faster one per row, but halves the number of work items: it
     # is taken when its items still fill the SMs (measured on the 8B layer: equal at 1,024 prompt tokens = 128
@@ -135,7 +134,7 @@ class GQAAttention(Part):
         if not bfloat16 or not self._flash_takes():
             return ()
         return ("attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.hd, self.H // self.G) \
-            and not (self.sink or self.softcap or self.chunk) else ("attention_flash",)
+            else ("attention_flash",)
 
     def _flash_takes(self) -> bool:
         """Whether the flash kernels know everything this mixer asks of the scores."""
@@ -205,8 +204,7 @@ class GQAAttention(Part):
     def step_tables(self, ctx):
         """Cuts the batch into the flash kernels' work items (csrc/attention_fast.py).  In a step whose shape must
         not change (a captured decode graph) every request's keys go to the same number of splits."""
-        return flash_step_tables(ctx, self.H, self.G, self.hd, self.window or 0, self.chunk, self._sm_count,
-                                 plain=not (self.sink or self.softcap or self.chunk))
+        return flash_step_tables(ctx, self.H, self.G, self.hd, self.window or 0, self.chunk, self._sm_count)
 
     def _plan(self, ctx):
         return flash_plan(ctx, self._tables_key)

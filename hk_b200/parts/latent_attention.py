@@ -74,7 +74,7 @@ class LatentAttention(Part):
         from .attention import flash_step_tables
         if self._wide:
             # items of at most 64 / H tokens, all heads of a token in one item; never the tcgen05 prompt kernels' tiles
-            return flash_step_tables(ctx, self.H, 1, self.r + self.dr, self.window or 0, 0, self._sm_count, plain=False)
+            return flash_step_tables(ctx, self.H, 1, self.r + self.dr, self.window or 0, 0, self._sm_count, tensor_prompt=False)
         return flash_step_tables(ctx, self.H, 1, self.r + self.dr, self.window or 0, 0, self._sm_count)
 
     def children(self):
