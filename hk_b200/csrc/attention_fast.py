@@ -283,9 +283,10 @@ def latent_supported(H: int, dk: int, dv: int) -> bool:
 
 
 def run_latent(q, pages, block_table, out, H: int, dk: int, dv: int, page_tokens: int, window: int, scale: float,
-               plan: FlashPlan) -> bool:
+               plan: FlashPlan, single_tokens: bool = False) -> bool:
     """out bf16 [n, H * dv] from q bf16 [n, H * dk] over the cache rows `pages` [pages, 1, page_tokens, dk]; the plan's
-    items hold at most 64 / H tokens each (a plan made with `plan_arrays(..., H, 1, ...)`)."""
+    items hold at most 64 / H tokens each (a plan made with `plan_arrays(..., H, 1, ...)`).  `single_tokens`: every item
+    holds one token (a decode step), which the kernel's decode variant takes."""
     from . import ops
     if not latent_supported(H, dk, dv) or plan is None:
         return False
@@ -297,7 +298,7 @@ def run_latent(q, pages, block_table, out, H: int, dk: int, dv: int, page_tokens
         part_ml = torch.empty((plan.n_parts, LATENT_ROWS, 2), dtype=torch.float32, device=q.device)
     code = lib.hk_attention_latent(_ptr(q), _ptr(pages), _ptr(block_table), int(block_table.shape[1]), _ptr(plan.items),
                                    plan.n_items, _ptr(out), _ptr(part_o), _ptr(part_ml), H, dk, dv, int(page_tokens), int(window),
-                                   ctypes.c_float(scale * math.log2(math.e)), stream)
+                                   ctypes.c_float(scale * math.log2(math.e)), 1 if single_tokens else 0, stream)
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "latent attention")

@@ -302,6 +302,250 @@ latent_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, 
   }
 }
 
+// Decode variant: the items of a step of single tokens fill 16 * MT of a tile's rows (one token, H <= 16 * MT heads), so
+// the work of a key tile is spread the other way: tiles of 64 cache rows, and for the scores each of the eight warps takes
+// 8 keys against all rows; the row maxima and the probabilities go through shared memory (CTA-wide barriers); for the
+// weighted values each warp takes an eighth of the value columns over all 64 keys.  Per key a warp then issues an eighth
+// of the products that the prompt variant's busiest warp does, and no warp idles.
+constexpr int DTK = 64;       // keys of a tile
+constexpr int DPLD = DTK + 8;
+
+size_t latent_decode_smem(int DK, int MT) {
+  const size_t LD = (size_t)DK + 8;
+  return (16 * MT * LD + 2 * DTK * LD + 16 * MT * DPLD) * sizeof(bf16) + (8 + 8) * 16 * MT * sizeof(float) + 2 * DTK * sizeof(int);
+}
+
+// MT: 16-row tiles (1: up to 16 heads, 2: up to 32); DVC: value columns per warp (DV <= 8 * DVC)
+template <int MT, int DVC>
+__global__ void __launch_bounds__(256, 1)
+latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, const int* __restrict__ block_table,
+                     int table_stride, const Item* __restrict__ items, bf16* __restrict__ out, float* __restrict__ part_o,
+                     float* __restrict__ part_ml, int H, int DK, int DV, int page_tokens, int window, float scale_log2) {
+  constexpr int R = 16 * MT;
+  const int LD = DK + 8;
+  const int CPR = DK / 8;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [R][LD]
+  bf16* ks = qs + R * LD;                                       // [2][DTK][LD]
+  bf16* ps = ks + 2 * DTK * LD;                                 // [R][DPLD]
+  float* mx = reinterpret_cast<float*>(ps + R * DPLD);          // [8][R] row maxima of the eight key slices
+  float* ls = mx + 8 * R;                                       // [8][R] row sums of the eight key slices
+  int* tile_rows = reinterpret_cast<int*>(ls + 8 * R);          // [2][DTK]
+
+  const Item it = items[blockIdx.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qr = lane >> 2, qt = lane & 3;
+  const int mi = lane >> 3, r8 = lane & 7;
+  const int* bt = block_table + (size_t)it.slot * table_stride;
+  const int pos = it.pos0;                                      // one token
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+
+  for (int r = warp; r < R; r += 8) {
+    const bool ok = r < H;
+    const bf16* src = q + ((size_t)it.q_row0 * H + (ok ? r : 0)) * DK;
+    for (int c = lane; c < CPR; c += 32) cp_async16(qs + r * LD + c * 8, src + c * 8, ok);
+  }
+
+  float o[MT][DVC / 8][4];
+  float m[MT][2], l[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int n = 0; n < DVC / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[mt][n][e] = 0.f;
+    m[mt][0] = m[mt][1] = -CUDART_INF_F;
+    l[mt][0] = l[mt][1] = 0.f;
+  }
+
+  const int t_begin = it.kv_lo / DTK;
+  const int t_end = (it.kv_hi + DTK - 1) / DTK;
+
+  auto load_tile = [&](int t, int stage) {
+    bf16* kd = ks + stage * DTK * LD;
+    int* pg = tile_rows + stage * DTK;
+    if (threadIdx.x < DTK) {
+      const int j = t * DTK + threadIdx.x;
+      int row_of_key = -1;
+      if (j >= it.kv_lo && j < it.kv_hi) {
+        const int pi = j / page_tokens;
+        const int page = bt[pi];
+        if (page >= 0) row_of_key = page * page_tokens + (j - pi * page_tokens);
+      }
+      pg[threadIdx.x] = row_of_key;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = warp; r < DTK; r += 8) {
+      const int row_of_key = pg[r];
+      const bool ok = row_of_key >= 0;
+      const bf16* src = pages + (ok ? (size_t)row_of_key * DK : 0);
+      for (int c = lane; c < CPR; c += 32) cp_async16(kd + r * LD + c * 8, src + c * 8, ok);
+    }
+  };
+
+  if (t_begin < t_end) load_tile(t_begin, 0);
+  cp_async_commit();
+  for (int t = t_begin; t < t_end; ++t) {
+    const int stage = (t - t_begin) & 1;
+    if (t + 1 < t_end) load_tile(t + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const bf16* kt = ks + stage * DTK * LD;
+
+    // ---- scores: all rows against this warp's 8 keys; two K slices of 16 columns per fragment load of the keys
+    float sp[2][MT][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sp[u][mt][e] = 0.f;
+    // x4 of the keys: matrices (k 0-7, k 8-15, k 16-23, k 24-31) of the warp's 8 keys -> b0, b1 of two K slices
+    const bf16* kb = kt + (warp * 8 + r8) * LD + mi * 8;
+    const int kpairs = DK / 32;                    // DK is a multiple of 16: a last single slice is handled below
+    for (int kp = 0; kp < kpairs; ++kp) {
+      uint32_t b[4];
+      ldmatrix_x4(b, kb + kp * 32);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t a0[4], a1[4];
+        const bf16* qa = qs + (mt * 16 + r8 + (mi & 1) * 8) * LD + (mi >> 1) * 8 + kp * 32;
+        ldmatrix_x4(a0, qa);
+        ldmatrix_x4(a1, qa + 16);
+        mma_bf16(sp[0][mt], a0, b[0], b[1]);
+        mma_bf16(sp[1][mt], a1, b[2], b[3]);
+      }
+    }
+    if (DK & 16) {                                 // the odd slice: its fragment load reads 16 columns past DK only as padding rows allow
+      uint32_t b[4];
+      const bf16* kl = kt + (warp * 8 + r8) * LD + (mi & 1) * 8 + kpairs * 32;     // matrices 2, 3 repeat 0, 1
+      ldmatrix_x4(b, kl);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t a0[4];
+        ldmatrix_x4(a0, qs + (mt * 16 + r8 + (mi & 1) * 8) * LD + (mi >> 1) * 8 + kpairs * 32);
+        mma_bf16(sp[0][mt], a0, b[0], b[1]);
+      }
+    }
+    float s[MT][4];
+    const int j0 = t * DTK + warp * 8 + 2 * qt;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      float mt0 = -CUDART_INF_F, mt1 = -CUDART_INF_F;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + (e & 1);
+        const bool ok = j >= lo && j <= pos && j >= it.kv_lo && j < it.kv_hi;
+        s[mt][e] = ok ? (sp[0][mt][e] + sp[1][mt][e]) * scale_log2 : -CUDART_INF_F;
+      }
+      mt0 = fmaxf(s[mt][0], s[mt][1]);
+      mt1 = fmaxf(s[mt][2], s[mt][3]);
+      mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 1));
+      mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 2));
+      mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 1));
+      mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 2));
+      if (qt == 0) {
+        mx[warp * R + mt * 16 + qr] = mt0;
+        mx[warp * R + mt * 16 + qr + 8] = mt1;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      float msafe[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = mt * 16 + qr + 8 * i;
+        float mn = m[mt][i];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) mn = fmaxf(mn, mx[w * R + r]);
+        msafe[i] = mn == -CUDART_INF_F ? 0.f : mn;
+        const float corr = exp2f(m[mt][i] - msafe[i]);
+        m[mt][i] = mn;
+        l[mt][i] *= corr;
+#pragma unroll
+        for (int n = 0; n < DVC / 8; ++n) {
+          o[mt][n][2 * i] *= corr;
+          o[mt][n][2 * i + 1] *= corr;
+        }
+      }
+      float p[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        p[e] = exp2f(s[mt][e] - msafe[e >> 1]);
+        l[mt][e >> 1] += p[e];
+      }
+      const int col = warp * 8 + 2 * qt;
+      *reinterpret_cast<uint32_t*>(ps + (mt * 16 + qr) * DPLD + col) = pack_bf16(p[0], p[1]);
+      *reinterpret_cast<uint32_t*>(ps + (mt * 16 + qr + 8) * DPLD + col) = pack_bf16(p[2], p[3]);
+    }
+    __syncthreads();
+    // ---- weighted values: all 64 keys, this warp's DVC value columns
+#pragma unroll
+    for (int kk = 0; kk < DTK / 16; ++kk) {
+      uint32_t pf[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(pf[mt], ps + (mt * 16 + r8 + (mi & 1) * 8) * DPLD + (mi >> 1) * 8 + kk * 16);
+      const bf16* vb = kt + (kk * 16 + (mi & 1) * 8 + r8) * LD + warp * DVC + (mi >> 1) * 8;
+#pragma unroll
+      for (int dp = 0; dp < DVC / 16; ++dp) {
+        if (warp * DVC + dp * 16 < DV) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, vb + dp * 16);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_bf16(o[mt][2 * dp], pf[mt], b[0], b[1]);
+            mma_bf16(o[mt][2 * dp + 1], pf[mt], b[2], b[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();   // the stage, the maxima and the probability tile are free again
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float v = l[mt][i];
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      if (qt == 0) ls[warp * R + mt * 16 + qr + 8 * i] = v;
+    }
+  __syncthreads();
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = mt * 16 + qr + 8 * i;
+      if (r >= H) continue;
+      float lt = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) lt += ls[w * R + r];
+      if (it.part < 0) {
+        bf16* op = out + ((size_t)it.q_row0 * H + r) * DV;
+        const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+#pragma unroll
+        for (int n = 0; n < DVC / 8; ++n) {
+          const int d = warp * DVC + n * 8 + 2 * qt;
+          if (d < DV) *reinterpret_cast<uint32_t*>(op + d) = pack_bf16(o[mt][n][2 * i] * inv, o[mt][n][2 * i + 1] * inv);
+        }
+      } else {
+        const size_t base = (size_t)it.part * ROWS + r;
+        float* po = part_o + base * DV;
+#pragma unroll
+        for (int n = 0; n < DVC / 8; ++n) {
+          const int d = warp * DVC + n * 8 + 2 * qt;
+          if (d < DV) *reinterpret_cast<float2*>(po + d) = make_float2(o[mt][n][2 * i], o[mt][n][2 * i + 1]);
+        }
+        if (warp == 0 && qt == 0) *reinterpret_cast<float2*>(part_ml + base * 2) = make_float2(m[mt][i], lt);
+      }
+    }
+}
+
 // Merges the partials of every (token, head) whose keys were split: partial s of token t sits at row
 // (first[t] + s) * ROWS + row0[t] + head.  One warp per (token, head); the partials are added in split order.
 __global__ void latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -353,19 +597,43 @@ int launch_latent(const void* q, const void* pages, const int* bt, int stride, c
   return hk_launch_status();
 }
 
+template <int MT, int DVC>
+int launch_latent_decode(const void* q, const void* pages, const int* bt, int stride, const void* items, int n_items, void* out,
+                         float* part_o, float* part_ml, int H, int DK, int DV, int pt, int window, float scale_log2, cudaStream_t s) {
+  const size_t smem = latent_decode_smem(DK, MT);
+  static HkSmemCache allowed = {};
+  if (int e = hk_allow_smem(latent_decode_kernel<MT, DVC>, smem, allowed)) return e;
+  latent_decode_kernel<MT, DVC><<<(unsigned)n_items, 256, smem, s>>>((const bf16*)q, (const bf16*)pages, bt, stride, (const Item*)items,
+                                                                     (bf16*)out, part_o, part_ml, H, DK, DV, pt, window, scale_log2);
+  return hk_launch_status();
+}
+
 }  // namespace
 
 // q bf16 [n, H, DK]; pages bf16 [pages, 1, page_tokens, DK]; out bf16 [n, H, DV]; items as for the flash kernels, an item
 // holding at most 64 / H query tokens; part_o [parts, 64, DV] and part_ml [parts, 64, 2] are fp32 scratch for items
-// with part >= 0; scale_log2 = scale * log2(e).
+// with part >= 0; scale_log2 = scale * log2(e).  single_tokens = 1 says that every item holds ONE token (a decode
+// step): with up to 32 heads the variant that spreads a tile's keys over all warps takes it.
 HK_API int hk_attention_latent(const void* q, const void* pages, const int* block_table, int table_stride, const void* items,
                                int n_items, void* out, float* part_o, float* part_ml, int H, int DK, int DV, int page_tokens,
-                               int window, float scale_log2, void* stream) {
+                               int window, float scale_log2, int single_tokens, void* stream) {
   if (n_items <= 0) return 0;
   if (H < 1 || H > ROWS || DK < 16 || DK > 576 || (DK & 15) || DV < 16 || DV > DK || DV > 512 || (DV & 15) || page_tokens < 1)
     return HK_ERR_UNSUPPORTED;
   if (((uintptr_t)q | (uintptr_t)pages | (uintptr_t)out) & 15) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
+  if (single_tokens && H <= 32) {
+#define HK_ARGS q, pages, block_table, table_stride, items, n_items, out, part_o, part_ml, H, DK, DV, page_tokens, window, scale_log2, s
+    if (H <= 16) {
+      if (DV <= 128) return launch_latent_decode<1, 16>(HK_ARGS);
+      if (DV <= 256) return launch_latent_decode<1, 32>(HK_ARGS);
+      return launch_latent_decode<1, 64>(HK_ARGS);
+    }
+    if (DV <= 128) return launch_latent_decode<2, 16>(HK_ARGS);
+    if (DV <= 256) return launch_latent_decode<2, 32>(HK_ARGS);
+    return launch_latent_decode<2, 64>(HK_ARGS);
+#undef HK_ARGS
+  }
   if (DV <= 128)
     return launch_latent<64>(q, pages, block_table, table_stride, items, n_items, out, part_o, part_ml, H, DK, DV, page_tokens, window, scale_log2, s);
   if (DV <= 256)

@@ -349,7 +349,7 @@ def padodra_kernel_points(width: int, n: int, context: int, peaks: dict) -> dict
     fixed_l = attention_fast.decode_splits(n, 1, sm) if decode else 0
     plan_l = attention_fast.build_plan(slots, q_starts, q_lens, starts, n, 0, H, 1, sm, up, fixed_splits=fixed_l,
                                        max_context=context + 64 if decode else 0, prefill_rows=64)
-    us = _time_kernel(lambda: attention_fast.run_latent(ql, rows_l, table, lat, H, dk, r, pt, 0, 192 ** -0.5, plan_l))
+    us = _time_kernel(lambda: attention_fast.run_latent(ql, rows_l, table, lat, H, dk, r, pt, 0, 192 ** -0.5, plan_l, single_tokens=decode))
     note("latent attention (rows of 576, values of 512)", us, (n * (context + 1) if decode else n) * dk * 2 + n * H * (dk + r) * 2,
          2.0 * pairs_plain * H * (dk + r), tc, like="attention (Qwen3)")
     proj = torch.randn(n, H * (dn + dr) + dk + H * dv, device=dev)

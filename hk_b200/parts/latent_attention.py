@@ -141,7 +141,8 @@ class LatentAttention(Part):
             from ..csrc import attention_fast
             lat = torch.empty((n, H * r), dtype=dt, device=dev)
             if attention_fast.run_latent(q_full, cache.k_pages, cache.block_table, lat, H, r + dr, r, cache.page_tokens,
-                                         self.window or 0, self.scale, plan):
+                                         self.window or 0, self.scale, plan,
+                                         single_tokens=all(int(c) == 1 for c in ctx.q_lens)):
                 lat = lat.view(n, H, r)
             else:
                 lat = None
