@@ -68,7 +68,7 @@ def under_every_cut(part, entry, plain, dtype, d, std=0.3, page_tokens=4, length
     (40, 4, 2, 16, 16, 0.3, 7, 4.0, M.banded(900.0, 8, 2.5, original=24)),       # blocks shorter than two pages
     (24, 3, 1, 12, 20, 0.4, 16, None, M.banded(10000.0, 12)),                    # values wider than keys, no cap
     (48, 2, 2, 34, 10, 0.2, None, 9.0, None),                                    # no mask, no rotation, sizes no multiple of 4
-    (64, 6, 2, 64, 64, 0.125, 23, 15.0, M.banded(50000.0, 64, 8.0, low=0.5, high=3.0, original=48)),
+    (64, 6, 2, 64, 64, 0.125, 23, 15.0, M.banded(60000.0, 64, 8.0, low=0.5, high=3.0, original=48)),
     (32, 1, 1, 136, 72, 0.1, 5, 2.0, M.banded(300.0, 30, 4.0, original=16)),     # one wide head
     (40, 5, 5, 8, 8, 0.5, 1000, 50.0, M.banded(100.0, 8)),                       # a block no request reaches
 ])
