@@ -179,6 +179,8 @@ def test_the_sink_takes_its_share_per_head(dtype):
     (48, 5, 6, 6, 14, 22, 0.35, M.ramped(300.0, 6, 5.0, original=32)),                         # nothing a multiple of 4
     (32, 1, 24, 8, 40, 300, 0.1, M.ramped(10000.0, 8, 2.0, original=8)),                       # one head, a cache row above 256
     (32, 2, 10, 16, 10, 12, 0.3, None),                                                        # no rotation at all
+    (40, 3, 8, 16, 10, 64, 0.2, M.ramped(2000.0, 16, 2.0, original=24)),                       # a cache row of 80: the flash kernels' sizes
+    (32, 2, 16, 16, 8, 32, 0.25, M.ramped(2000.0, 8)),                                         # a cache row of 48, part of the rotated dims turned
     # cache rows wider than a flash head (multiples of 16): the kernel with the query tile in shared memory
     (64, 4, 16, 16, 24, 176, 0.1, M.ramped(10000.0, 16, 4.0, original=32)),                   # values over 2 x 128 columns
     (48, 3, 32, 64, 16, 512, 0.05, M.ramped(10000.0, 64, 8.0, original=64)),                  # the widest row: 576, values 512
