@@ -41,12 +41,6 @@ def supported(hd: int, group: int) -> bool:
     return hd % 16 == 0 and 16 <= hd <= MAX_HD and group <= 64
 
 
-def options_supported(softcap: float, chunk: int, sink_weights: bool) -> bool:
-    """Whether the flash kernels know these options of the scores (a bound on the scores, a block-wise mask, a learned
-    score for the sink): all of them do (the mma.sync and the tcgen05 prompt kernels, both decode kernels)."""
-    return True
-
-
 def tc_prefill_supported(hd: int, group: int) -> bool:
     return hd in (64, 128) and group <= 128
 

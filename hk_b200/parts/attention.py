@@ -137,10 +137,9 @@ class GQAAttention(Part):
             else ("attention_flash",)
 
     def _flash_takes(self) -> bool:
-        """Whether the flash kernels know everything this mixer asks of the scores."""
+        """Whether the flash kernels take this mixer's sizes (they know every option of the scores: sink, cap, blocks)."""
         from ..csrc import attention_fast
-        return self.vd == self.hd and attention_fast.supported(self.hd, self.H // self.G) \
-            and attention_fast.options_supported(self.softcap, self.chunk, self.sink_weights)
+        return self.vd == self.hd and attention_fast.supported(self.hd, self.H // self.G)
 
     def children(self):
         return (self.position,) if self.position is not None else ()

@@ -117,6 +117,32 @@ class LatentAttention(Part):
             self._tables_key = ("latent_attention_items", self.window or 0, self.H, self.r + self.dr)
             self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
 
+    def _attend(self, q_full: torch.Tensor, ctx, cache) -> torch.Tensor:
+        """The attention over the cache rows: a view [n, H, kv_rank] of the heads' latent sums.  In bfloat16 a tensor-core
+        kernel takes it where one knows the row's size; else (and in 32-bit) the generic kernel."""
+        from .attention import flash_plan
+        n, dev, dt = q_full.shape[0], q_full.device, q_full.dtype
+        H, dr, r = self.H, self.dr, self.r
+        plan = flash_plan(ctx, self._tables_key) if dt == torch.bfloat16 and ops.forced("attention") != "generic" else None
+        if plan is not None and self._wide:
+            from ..csrc import attention_fast
+            lat = torch.empty((n, H * r), dtype=dt, device=dev)
+            # which variant runs depends on the batch's shape alone (single tokens or not), as a captured step's launches must
+            if attention_fast.run_latent(q_full, cache.k_pages, cache.block_table, lat, H, r + dr, r, cache.page_tokens,
+                                         self.window or 0, self.scale, plan,
+                                         single_tokens=all(int(c) == 1 for c in ctx.q_lens)):
+                return lat.view(n, H, r)
+        elif plan is not None:
+            # the flash kernels, with the cache rows as keys AND values: the first r dims of a head's result are its latent sums
+            wide = torch.empty((n, H * (r + dr)), dtype=dt, device=dev)
+            ops.paged_attention(q_full, cache.k_pages, cache.k_pages, cache.block_table, ctx.positions, ctx.slot_of_token, wide,
+                                H, 1, r + dr, cache.page_tokens, self.window or 0, self.scale, plan=plan)
+            return wide.view(n, H, r + dr)[:, :, :r]
+        lat = torch.empty((n, H * r), dtype=dt, device=dev)
+        ops.paged_attention(q_full, cache.k_pages, None, cache.block_table, ctx.positions, ctx.slot_of_token, lat,
+                            H, 1, r + dr, cache.page_tokens, self.window or 0, self.scale)
+        return lat.view(n, H, r)
+
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
                 accumulate: bool = True) -> None:
         n, dev, dt = xb.shape[0], xb.device, xb.dtype
@@ -134,31 +160,7 @@ class LatentAttention(Part):
                         ctx.slot_of_token, cache.block_table, cache.k_pages, H, dn, dr, r, cache.page_tokens,
                         write_kv=write_cache)
         ops.gemm_heads(q_plain.view(n, H, dn), self.w_uk_t, q_full.view(n, H, r + dr)[:, :, :r], H)
-        from .attention import flash_plan
-        plan = flash_plan(ctx, self._tables_key) if dt == torch.bfloat16 and ops.forced("attention") != "generic" else None
-        lat = None
-        if plan is not None and self._wide:
-            from ..csrc import attention_fast
-            lat = torch.empty((n, H * r), dtype=dt, device=dev)
-            if attention_fast.run_latent(q_full, cache.k_pages, cache.block_table, lat, H, r + dr, r, cache.page_tokens,
-                                         self.window or 0, self.scale, plan,
-                                         single_tokens=all(int(c) == 1 for c in ctx.q_lens)):
-                lat = lat.view(n, H, r)
-            else:
-                lat = None
-        if lat is not None:
-            pass
-        elif plan is not None and not self._wide:
-            # the flash kernels, with the cache rows as keys AND values: the result's first r dims per head are the latent sums
-            wide = torch.empty((n, H * (r + dr)), dtype=dt, device=dev)
-            ops.paged_attention(q_full, cache.k_pages, cache.k_pages, cache.block_table, ctx.positions, ctx.slot_of_token, wide,
-                                H, 1, r + dr, cache.page_tokens, self.window or 0, self.scale, plan=plan)
-            lat = wide.view(n, H, r + dr)[:, :, :r]
-        else:
-            lat = torch.empty((n, H * r), dtype=dt, device=dev)
-            ops.paged_attention(q_full, cache.k_pages, None, cache.block_table, ctx.positions, ctx.slot_of_token, lat,
-                                H, 1, r + dr, cache.page_tokens, self.window or 0, self.scale)
-            lat = lat.view(n, H, r)
+        lat = self._attend(q_full, ctx, cache)                  # [n, H, r]: sum_j p_j c_j per head
         att = torch.empty((n, H * vd), dtype=dt, device=dev)
         if self.gate:
             o = torch.empty((n, H * vd), dtype=torch.float32, device=dev)
