@@ -85,11 +85,13 @@ HK_API int hk_gemm_generic(const void* a, const void* w, int dtype, float* out, 
 // out[t, h, :N] = a[t, h, :K] * w[h]^T for every head h: w is [heads][N][K]; a's and out's rows of one token lie
 // `lda` / `ldo` elements apart and their heads `a_head` / `o_head` elements apart (so the output may be a column
 // slice of wider rows).  The output takes the storage type or fp32.  Same tiles and summation order as above, the
-// head in blockIdx.z.
+// head in blockIdx.z.  With `gate` (fp32 logits, row stride gate_ld, head h at column h * N) the result is multiplied
+// by sigmoid(gate).
 template <typename T, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_heads_kernel(const T* __restrict__ a, const T* __restrict__ w, TO* __restrict__ out, int M, int N, int K,
-                  long long lda, long long a_head, long long ldo, long long o_head) {
+                  long long lda, long long a_head, long long ldo, long long o_head, const float* __restrict__ gate,
+                  long long gate_ld) {
   __shared__ float As[GG_BK][GG_BM + 4];
   __shared__ float Ws[GG_BK][GG_BN + 4];
   const int tid = threadIdx.x, h = blockIdx.z;
@@ -134,23 +136,27 @@ gemm_heads_kernel(const T* __restrict__ a, const T* __restrict__ w, TO* __restri
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       int gn = n0 + tx * 4 + j;
-      if (gn < N) out[(size_t)gm * ldo + gn] = from_f32<TO>(acc[i][j]);
+      if (gn >= N) continue;
+      float v = acc[i][j];
+      if (gate) v /= 1.0f + expf(-gate[(size_t)gm * gate_ld + (size_t)h * N + gn]);
+      out[(size_t)gm * ldo + gn] = from_f32<TO>(v);
     }
   }
 }
 
 HK_API int hk_gemm_heads(const void* a, const void* w, int dtype, void* out, int out_dtype, int M, int N, int K, int heads,
-                         long long lda, long long a_head, long long ldo, long long o_head, void* stream) {
+                         long long lda, long long a_head, long long ldo, long long o_head, const float* gate, long long gate_ld,
+                         void* stream) {
   if (M <= 0 || N <= 0 || heads <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid((N + GG_BN - 1) / GG_BN, (M + GG_BM - 1) / GG_BM, heads);
   if (grid.y > 65535 || grid.z > 65535) return HK_ERR_UNSUPPORTED;
   if (dtype == HK_F32 && out_dtype == HK_F32)
-    gemm_heads_kernel<float, float><<<grid, 256, 0, s>>>((const float*)a, (const float*)w, (float*)out, M, N, K, lda, a_head, ldo, o_head);
+    gemm_heads_kernel<float, float><<<grid, 256, 0, s>>>((const float*)a, (const float*)w, (float*)out, M, N, K, lda, a_head, ldo, o_head, gate, gate_ld);
   else if (dtype == HK_BF16 && out_dtype == HK_BF16)
-    gemm_heads_kernel<bf16, bf16><<<grid, 256, 0, s>>>((const bf16*)a, (const bf16*)w, (bf16*)out, M, N, K, lda, a_head, ldo, o_head);
+    gemm_heads_kernel<bf16, bf16><<<grid, 256, 0, s>>>((const bf16*)a, (const bf16*)w, (bf16*)out, M, N, K, lda, a_head, ldo, o_head, gate, gate_ld);
   else if (dtype == HK_BF16 && out_dtype == HK_F32)
-    gemm_heads_kernel<bf16, float><<<grid, 256, 0, s>>>((const bf16*)a, (const bf16*)w, (float*)out, M, N, K, lda, a_head, ldo, o_head);
+    gemm_heads_kernel<bf16, float><<<grid, 256, 0, s>>>((const bf16*)a, (const bf16*)w, (float*)out, M, N, K, lda, a_head, ldo, o_head, gate, gate_ld);
   else
     return HK_ERR_UNSUPPORTED;
   return hk_launch_status();

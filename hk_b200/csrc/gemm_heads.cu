@@ -4,15 +4,17 @@
 // tcgen05 kernel's tiles and too many for a launch apiece.
 //
 // A CTA of four warps computes 64 rows x 64 columns of one head (blockIdx.z): each warp 16 rows x 64 columns on
-// mma.sync.m16n8k16 (bf16 in, fp32 accumulation in registers), operands through a two-stage cp.async ring of 32-wide
+// mma.sync.m16n8k16 (bf16 in, fp32 accumulation in registers), operands through a two-stage cp.async ring of 64-wide
 // K slices read with ldmatrix.  a's and out's rows and heads lie any number of elements apart (multiples of 8 for
 // a, of 2 for out), so either may be a column slice of wider rows; out is bf16 or fp32.  Each output element sums
 // k = 0..K-1 in one order whatever the batch, so a row's result does not depend on what else is in the step.
+// With `gate` (fp32 logits [M, >= heads * N], row stride gate_ld, head h at column h * N) the result is multiplied by
+// sigmoid(gate) in the epilogue: a mixer's output gate without a kernel of its own.
 #include "common.cuh"
 
 namespace {
 
-constexpr int BM = 64, BN = 64, BK = 32, LDS = BK + 8;
+constexpr int BM = 64, BN = 64, BK = 64, LDS = BK + 8;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -43,7 +45,8 @@ __device__ __forceinline__ void store2<bf16>(bf16* p, float x, float y) { *reint
 template <typename TO>
 __global__ void __launch_bounds__(128)
 gemm_heads_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, TO* __restrict__ out, int M, int N, int K,
-                      long long lda, long long a_head, long long ldo, long long o_head) {
+                      long long lda, long long a_head, long long ldo, long long o_head, const float* __restrict__ gate,
+                      long long gate_ld) {
   __shared__ __align__(16) bf16 As[2][BM][LDS];
   __shared__ __align__(16) bf16 Ws[2][BN][LDS];
   pdl_launch_dependents();
@@ -61,11 +64,11 @@ gemm_heads_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, TO
     for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
 
   auto load = [&](int k0, int stage) {
-    // 64 rows x 4 chunks of 8 for each operand: 256 chunks, two a thread
+    // 64 rows x 8 chunks of 8 for each operand: 512 chunks, four a thread
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       const int idx = threadIdx.x + i * 128;
-      const int r = idx >> 2, c = (idx & 3) * 8;
+      const int r = idx >> 3, c = (idx & 7) * 8;
       const bool ka = k0 + c < K;
       const bool oka = ka && m0 + r < M, okw = ka && n0 + r < N;
       cp_async16(&As[stage][r][c], a + (oka ? (size_t)(m0 + r) * lda + k0 + c : 0), oka);
@@ -100,11 +103,17 @@ gemm_heads_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, TO
     const int gm = m0 + warp * 16 + qr + 8 * i;
     if (gm >= M) continue;
     TO* o = out + (size_t)gm * ldo;
+    const float* gr = gate ? gate + (size_t)gm * gate_ld + (size_t)h * N : nullptr;
 #pragma unroll
     for (int n = 0; n < BN / 8; ++n) {
       const int gn = n0 + n * 8 + 2 * qt;
-      if (gn + 1 < N) store2<TO>(o + gn, acc[n][2 * i], acc[n][2 * i + 1]);
-      else if (gn < N) o[gn] = from_f32<TO>(acc[n][2 * i]);
+      float x = acc[n][2 * i], y = acc[n][2 * i + 1];
+      if (gr) {
+        if (gn < N) x /= 1.0f + expf(-gr[gn]);
+        if (gn + 1 < N) y /= 1.0f + expf(-gr[gn + 1]);
+      }
+      if (gn + 1 < N) store2<TO>(o + gn, x, y);
+      else if (gn < N) o[gn] = from_f32<TO>(x);
     }
   }
 }
@@ -114,7 +123,7 @@ gemm_heads_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, TO
 // Refuses (HK_ERR_UNSUPPORTED) what the 16-byte copies and paired stores cannot take: K, lda or a_head no multiple of
 // 8, ldo or o_head odd, operands not 16-byte (out: 8-byte for fp32, 4-byte for bf16) aligned.
 HK_API int hk_gemm_heads_mma(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K, int heads, long long lda,
-                             long long a_head, long long ldo, long long o_head, void* stream) {
+                             long long a_head, long long ldo, long long o_head, const float* gate, long long gate_ld, void* stream) {
   if (M <= 0 || N <= 0 || heads <= 0) return 0;
   if (K <= 0 || (K & 7) || (lda & 7) || (a_head & 7) || (ldo & 1) || (o_head & 1)) return HK_ERR_UNSUPPORTED;
   if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & (out_dtype == HK_F32 ? 7 : 3))) return HK_ERR_UNSUPPORTED;
@@ -123,9 +132,9 @@ HK_API int hk_gemm_heads_mma(const void* a, const void* w, void* out, int out_dt
   cudaStream_t s = (cudaStream_t)stream;
   if (out_dtype == HK_F32)
     return hk_launch_pdl(gemm_heads_mma_kernel<float>, grid, dim3(128), 0, s, (const bf16*)a, (const bf16*)w, (float*)out, M, N, K, lda,
-                         a_head, ldo, o_head);
+                         a_head, ldo, o_head, gate, gate_ld);
   if (out_dtype == HK_BF16)
     return hk_launch_pdl(gemm_heads_mma_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)a, (const bf16*)w, (bf16*)out, M, N, K, lda,
-                         a_head, ldo, o_head);
+                         a_head, ldo, o_head, gate, gate_ld);
   return HK_ERR_UNSUPPORTED;
 }

@@ -436,10 +436,11 @@ def latent_prep(proj, q_plain, q_full, c_weight, eps, cos, sin, rotary_dim, pair
         1 if write_kv else 0, _stream()), "latent_prep")
 
 
-def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_heads: int) -> None:
+def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_heads: int, gate: Optional[torch.Tensor] = None) -> None:
     """One small product per head: out[t, h, :N] = a[t, h, :K] @ w[h]^T for w [H, N, K].  `a` and `out` are 3-D views
     [n, H, K] and [n, H, N] with any row and head strides and unit stride along the last dimension (so either may be
-    a slice of wider heads).  out takes a's type or float32."""
+    a slice of wider heads).  out takes a's type or float32.  `gate` (a float32 column slice [n, H * N] of a projection's
+    output): the result is multiplied by sigmoid(gate), head h reading columns h * N .. of it."""
     H = n_heads
     for name, t in (("a", a), ("out", out)):
         if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dim() != 3 or t.stride(2) != 1 or t.shape[1] != H:
@@ -449,18 +450,23 @@ def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_heads: int
     N = out.shape[2]
     if tuple(w.shape) != (H, N, K) or out.shape[0] != n:
         raise KernelError("gemm_heads: shapes do not fit")
+    gate_ld = 0
+    if gate is not None:
+        gate_ld = _cols(gate, "gate", H * N)
+        if gate.shape[0] != n:
+            raise KernelError("gemm_heads: one row of gate logits per row")
     if a.dtype == torch.bfloat16 and _forced["gemm"] != "generic":
         lib = build.load("gemm_heads")
         code = lib.hk_gemm_heads_mma(_ptr(a), _ptr(w), _ptr(out), _dt(out), n, N, K, H, ctypes.c_longlong(a.stride(0)),
                                      ctypes.c_longlong(a.stride(1)), ctypes.c_longlong(out.stride(0)),
-                                     ctypes.c_longlong(out.stride(1)), _stream())
+                                     ctypes.c_longlong(out.stride(1)), _ptr(gate), ctypes.c_longlong(gate_ld), _stream())
         if code != _ERR_UNSUPPORTED:
             _check(code, "gemm_heads (mma)")
             return
     lib = build.load("gemm_generic")
     _check(lib.hk_gemm_heads(_ptr(a), _ptr(w), _dt(a), _ptr(out), _dt(out), n, N, K, H, ctypes.c_longlong(a.stride(0)),
                              ctypes.c_longlong(a.stride(1)), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)),
-                             _stream()), "gemm_heads")
+                             _ptr(gate), ctypes.c_longlong(gate_ld), _stream()), "gemm_heads")
 
 
 # ---- sampling -------------------------------------------------------------------------

@@ -372,8 +372,10 @@ def padodra_kernel_points(width: int, n: int, context: int, peaks: dict) -> dict
     us = _time_kernel(lambda: ops.gemm_heads(q_plain.view(n, H, dn), w_uk, ql.view(n, H, dk)[:, :, :r], H))
     note("query into the latent space (a product per head)", us, H * r * dn * 2 + n * H * (dn + r) * 2, 2.0 * n * H * r * dn, tc,
          like="dense product of equal FLOPs (Qwen3)")
-    us = _time_kernel(lambda: ops.gemm_heads(lat.view(n, H, r), w_uv, o.view(n, H, dv), H))
-    note("values out of the latent space (a product per head)", us, H * r * dv * 2 + n * H * (r * 2 + dv * 4), 2.0 * n * H * r * dv, tc,
+    glat = torch.randn(n, H * dv, device=dev)
+    ob = torch.empty(n, H * dv, dtype=torch.bfloat16, device=dev)
+    us = _time_kernel(lambda: ops.gemm_heads(lat.view(n, H, r), w_uv, ob.view(n, H, dv), H, gate=glat))
+    note("values out of the latent space, gated (a product per head)", us, H * r * dv * 2 + n * H * (r * 2 + dv * 6), 2.0 * n * H * r * dv, tc,
          like="dense product of equal FLOPs (Qwen3)")
     wd = (torch.randn(H * dn, r, device=dev) * 0.05).bfloat16()       # [N = H * 128, K = 512]: the same FLOPs as one of the two
     a2 = (torch.randn(n, r, device=dev) * 0.3).bfloat16()

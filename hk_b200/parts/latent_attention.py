@@ -162,12 +162,8 @@ class LatentAttention(Part):
         ops.gemm_heads(q_plain.view(n, H, dn), self.w_uk_t, q_full.view(n, H, r + dr)[:, :, :r], H)
         lat = self._attend(q_full, ctx, cache)                  # [n, H, r]: sum_j p_j c_j per head
         att = torch.empty((n, H * vd), dtype=dt, device=dev)
-        if self.gate:
-            o = torch.empty((n, H * vd), dtype=torch.float32, device=dev)
-            ops.gemm_heads(lat, self.w_uv, o.view(n, H, vd), H)
-            ops.sigmoid_gate(o, proj[:, H * (dn + dr) + r + dr:], att)
-        else:
-            ops.gemm_heads(lat, self.w_uv, att.view(n, H, vd), H)
+        # the values' up-projection per head, with the output gate in its epilogue
+        ops.gemm_heads(lat, self.w_uv, att.view(n, H, vd), H, gate=proj[:, H * (dn + dr) + r + dr:] if self.gate else None)
         ops.gemm(att, self.w_o, residual, accumulate=accumulate)
 
 

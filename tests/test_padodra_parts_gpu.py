@@ -13,6 +13,7 @@ from test_parts_gpu import DTYPES, IDS, bind_random
 
 pytestmark = pytest.mark.gpu
 EPS = 1e-5
+K_sigmoid = K.sigmoid
 
 
 def attention_part(d, H, G, dk, dv, scale, block=None, cap=None, rot=None, positions=1024):
@@ -302,6 +303,14 @@ def test_a_product_per_head_over_slices_of_wider_rows(dtype, n, H, K, N):
             again = torch.zeros((n, H, N), dtype=out_dtype, device="cuda")
             ops.gemm_heads(a_wide[:, :, :K], w, again, H)
         close(again.double().cpu().numpy(), want, dtype)
+        # with a gate in the epilogue: logits as a column slice of wider float32 rows
+        logits = torch.randn(n, H * N + 5, generator=g).cuda()
+        gated = want * K_sigmoid(logits[:, 5:].double().cpu().numpy()).reshape(n, H, N)
+        for kernel in (None, "generic"):
+            got = torch.zeros((n, H, N), dtype=out_dtype, device="cuda")
+            with ops.force(gemm=kernel):
+                ops.gemm_heads(a_wide[:, :, :K], w, got, H, gate=logits[:, 5:])
+            close(got.double().cpu().numpy(), gated, dtype)
 
 
 @pytest.mark.parametrize("d", [48, 512, 1000, 4096])
